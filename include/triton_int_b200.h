@@ -1,0 +1,152 @@
+/*
+ * triton_int_b200 -- C ABI of the sm_100a INT8 operator library.
+ *
+ * Plain pointers and sizes only; no exceptions cross this boundary.  Every entry
+ * point returns a ti_status, launches asynchronously on the given CUDA stream
+ * and never allocates memory the caller can see.  All data pointers are device
+ * pointers on the current device unless stated otherwise; there is no CPU path.
+ *
+ * Each declaration names the reference interface (file:line inside the
+ * reference project) that it replaces.
+ */
+#ifndef TRITON_INT_B200_H
+#define TRITON_INT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  TI_OK = 0,
+  TI_ERR_SHAPE = 1,       /* rank / extent mismatch (the reference raises AssertionError) */
+  TI_ERR_DTYPE = 2,
+  TI_ERR_ALIGN = 3,       /* a pointer or stride the requested path cannot take */
+  TI_ERR_DEVICE = 4,      /* null or non-device pointer, wrong architecture */
+  TI_ERR_TIMEOUT = 5,     /* a bounded device-side wait gave up (see ti_device_status) */
+  TI_ERR_CUDA = 6,        /* a CUDA runtime/driver call failed (see ti_last_error_string) */
+  TI_ERR_UNSUPPORTED = 7
+} ti_status;
+
+typedef enum { TI_I8 = 0, TI_I32 = 1, TI_F32 = 2, TI_F16 = 3, TI_BF16 = 4 } ti_dtype;
+
+/* float -> int8 policy of every quantising epilogue.
+ *   TI_ROUND_RNE_SAT    round half to even, saturate to [-128,127]
+ *   TI_ROUND_TRUNC_WRAP truncate toward zero, keep the low byte: the behaviour of
+ *                       the reference kernels' `.to(tl.int8)` (kernels/linear.py:254) */
+typedef enum { TI_ROUND_RNE_SAT = 0, TI_ROUND_TRUNC_WRAP = 1 } ti_rounding;
+
+typedef enum {
+  TI_EPI_I32 = 0,             /* C = acc (+ bias_i32)            kernels/linear.py:505-507,534; kernels/bmm.py:163-273 */
+  TI_EPI_SCALE = 1,           /* C = cast(alpha*f32(acc))        kernels/linear.py:107; kernels/bmm.py:414,562,710 */
+  TI_EPI_SCALE_BIAS = 2,      /* C = cast(beta*f32(bias) + alpha*f32(acc))   kernels/linear.py:225-227,247,254,674,817 */
+  TI_EPI_SCALE_BIAS_RELU = 3, /* C = max(cast_i8(...), 0)        kernels/linear.py:396 */
+  TI_EPI_GELU_Q = 4           /* C = cast_i8(gelu_tanh(alpha*f32(acc) + bias) * beta)   kernels/fused.py:184-187 */
+} ti_epilogue;
+
+typedef enum { TI_PATH_AUTO = 0, TI_PATH_TCGEN05 = 1, TI_PATH_GENERIC = 2 } ti_gemm_path;
+
+/*
+ * One int8 x int8 -> int32 GEMM / batched GEMM with a fused epilogue:
+ *     acc[b,m,n] = sum_k A[b,m,k] * B[b,n,k]          (B addressed through its strides)
+ * Replaces the 6 linear kernels of kernels/linear.py:24-853, the GELU-Q linear of
+ * kernels/fused.py:88-231 and the 5 BMM kernels of kernels/bmm.py:12-760.
+ * Strides are in elements.  A linear is batch == 1.  "s8n" operands ([N,K]) have
+ * b_stride_k == 1; "s8t" operands ([K,N]) have b_stride_n == 1.
+ * alpha/beta are DEVICE pointers to one float each (the reference reads its
+ * scales with tl.load, kernels/linear.py:227,247); NULL means 1.0.
+ */
+typedef struct {
+  const int8_t* a;
+  const int8_t* b;
+  void* c;
+  const void* bias;        /* [n], dtype bias_dtype; may be NULL (treated as 0) */
+  const float* alpha;
+  const float* beta;
+  int64_t m, n, k, batch;
+  int64_t a_stride_m, a_stride_k, a_stride_batch;
+  int64_t b_stride_n, b_stride_k, b_stride_batch;
+  int64_t c_stride_m, c_stride_n, c_stride_batch;
+  int32_t bias_dtype;      /* ti_dtype */
+  int32_t out_dtype;       /* ti_dtype */
+  int32_t epilogue;        /* ti_epilogue */
+  int32_t rounding;        /* ti_rounding */
+  int32_t path;            /* ti_gemm_path */
+  int32_t causal;          /* 1: skip output tiles with n0 > m0 + BM - 1 + (n - m) (never read by a causal softmax) */
+  void* stream;            /* cudaStream_t */
+} ti_gemm_params;
+
+int ti_gemm_i8(const ti_gemm_params* p);
+
+/*
+ * Row-wise normalisation family.  One struct covers
+ *   layer_norm_fwd_fused_single_pass_q      kernels/fused.py:235-382   (out int8)
+ *   layer_norm_fwd_fused_single_pass        kernels/fused.py:385-532   (out = input dtype)
+ *   skip_layer_norm_fwd_fused_single_pass   kernels/fused.py:535-693   (out2 = out + skip)
+ *   skip_layer_norm_fwd_fused_single_pass2  kernels/fused.py:696-862   (out and out2)
+ *   dq_add_layernorm_q                      functional/fused.py:6-15,27-32; nn/fused.py:59-78
+ * With x_dtype == TI_I32 the row is first dequantised and added to the residual:
+ *     r = residual_in + dq_scale * (x + bias_i32) ; residual_out = r ; y = LN(r).
+ * Strides are in elements; the column stride of x and out may differ from 1.
+ */
+typedef struct {
+  const void* x;
+  const float* residual_in;   /* fp32 [rows,n], row stride n; required when x_dtype == TI_I32 */
+  float* residual_out;        /* optional fp32 [rows,n] */
+  const int32_t* bias_i32;    /* optional [n], added to the int32 row before dequantisation */
+  const void* gamma;          /* [n] */
+  const void* beta;           /* [n] or NULL */
+  const void* skip;           /* [rows,n] in x's layout or NULL */
+  void* out;                  /* may be NULL when only out2 is wanted */
+  void* out2;                 /* out + skip, or NULL */
+  const float* dq_scale_dev;  /* optional device scalar overriding dq_scale */
+  int64_t rows, n;
+  int64_t x_row_stride, x_col_stride;
+  int64_t out_row_stride, out_col_stride;
+  float eps;
+  float dq_scale;
+  int32_t x_dtype;            /* TI_F32 / TI_F16 / TI_BF16 / TI_I32 */
+  int32_t param_dtype;        /* dtype of gamma/beta/skip */
+  int32_t out_dtype;          /* TI_I8 or a float dtype */
+  int32_t rounding;
+  int32_t rms;                /* 1: RMSNorm (kernels/fused.py:291-292) */
+  void* stream;
+} ti_layernorm_params;
+
+int ti_layernorm(const ti_layernorm_params* p);
+
+/* Stand-alone int8 GELU: y = cast_i8(gelu_tanh(in_scale * x) * out_mul), the
+ * formula of fast_geluQ (kernels/fused.py:76-79) that nn/fused.py:81-87 (GeLu_Q)
+ * was meant to expose.  x and y are contiguous, n_elems bytes each. */
+int ti_gelu_q(const int8_t* x, int8_t* y, int64_t n_elems, float in_scale, float out_mul,
+              int32_t rounding, void* stream);
+
+/* Causal softmax over the last dimension of fp32 scores, quantised to int8:
+ * p = cast_i8(out_mul * softmax(mask(s))), query row i sees keys j <= i + (n - m).
+ * The step a caller performs between bmm_s8t_s8n_f32t (kernels/bmm.py:428-464)
+ * and bmm_s8t_s8n_s8t (kernels/bmm.py:576-612); the reference leaves it to user
+ * code.  s is [batch,m,n] with row stride s_row_stride and batch stride
+ * s_batch_stride (elements), p likewise. causal == 0 gives a plain softmax. */
+int ti_softmax_q(const float* s, int8_t* p, int64_t batch, int64_t m, int64_t n,
+                 int64_t s_row_stride, int64_t s_batch_stride,
+                 int64_t p_row_stride, int64_t p_batch_stride,
+                 int32_t causal, float out_mul, int32_t rounding, void* stream);
+
+/* Reads and clears the device-side status word of the current device.  Non-zero
+ * means a bounded wait inside a kernel expired (bit 0: TMA producer, bit 1: MMA
+ * issuer, bit 2: epilogue).  Synchronises the device. */
+int ti_device_status(uint32_t* status_out);
+
+/* Library facts. */
+int ti_version(void);
+const char* ti_last_error_string(void);
+/* Number of kernels this library has launched since load (host-side counter). */
+int64_t ti_launch_count(void);
+/* 1 when the current device can run the tcgen05 path (compute capability 10.x). */
+int ti_device_supported(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRITON_INT_B200_H */
