@@ -1,0 +1,121 @@
+"""ctypes binding of the C ABI declared in include/triton_int_b200.h.
+
+The product path has no CPU fallback: if the CUDA library is missing and cannot
+be built, importing an operator raises; if a tensor is not on a CUDA device the
+call raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+from . import _build
+
+# ---- enums (mirror include/triton_int_b200.h) ----
+TI_OK, TI_ERR_SHAPE, TI_ERR_DTYPE, TI_ERR_ALIGN, TI_ERR_DEVICE, TI_ERR_TIMEOUT, TI_ERR_CUDA, TI_ERR_UNSUPPORTED = range(8)
+TI_I8, TI_I32, TI_F32, TI_F16, TI_BF16 = range(5)
+ROUND_RNE_SAT, ROUND_TRUNC_WRAP = 0, 1
+EPI_I32, EPI_SCALE, EPI_SCALE_BIAS, EPI_SCALE_BIAS_RELU, EPI_GELU_Q = range(5)
+PATH_AUTO, PATH_TCGEN05, PATH_GENERIC = range(3)
+
+DTYPE_CODE = {torch.int8: TI_I8, torch.int32: TI_I32, torch.float32: TI_F32,
+              torch.float16: TI_F16, torch.bfloat16: TI_BF16}
+
+EXPORTS = ["ti_gemm_i8", "ti_layernorm", "ti_gelu_q", "ti_softmax_q", "ti_device_status",
+           "ti_version", "ti_last_error_string", "ti_launch_count", "ti_device_supported"]
+
+
+class GemmParams(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p), ("bias", C.c_void_p),
+        ("alpha", C.c_void_p), ("beta", C.c_void_p),
+        ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64), ("batch", C.c_int64),
+        ("a_stride_m", C.c_int64), ("a_stride_k", C.c_int64), ("a_stride_batch", C.c_int64),
+        ("b_stride_n", C.c_int64), ("b_stride_k", C.c_int64), ("b_stride_batch", C.c_int64),
+        ("c_stride_m", C.c_int64), ("c_stride_n", C.c_int64), ("c_stride_batch", C.c_int64),
+        ("bias_dtype", C.c_int32), ("out_dtype", C.c_int32), ("epilogue", C.c_int32),
+        ("rounding", C.c_int32), ("path", C.c_int32), ("causal", C.c_int32),
+        ("stream", C.c_void_p),
+    ]
+
+
+class LayerNormParams(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("residual_in", C.c_void_p), ("residual_out", C.c_void_p),
+        ("bias_i32", C.c_void_p), ("gamma", C.c_void_p), ("beta", C.c_void_p), ("skip", C.c_void_p),
+        ("out", C.c_void_p), ("out2", C.c_void_p), ("dq_scale_dev", C.c_void_p),
+        ("rows", C.c_int64), ("n", C.c_int64),
+        ("x_row_stride", C.c_int64), ("x_col_stride", C.c_int64),
+        ("out_row_stride", C.c_int64), ("out_col_stride", C.c_int64),
+        ("eps", C.c_float), ("dq_scale", C.c_float),
+        ("x_dtype", C.c_int32), ("param_dtype", C.c_int32), ("out_dtype", C.c_int32),
+        ("rounding", C.c_int32), ("rms", C.c_int32),
+        ("stream", C.c_void_p),
+    ]
+
+
+_LIB = None
+
+
+def lib_path() -> str:
+    return _build.LIB_PATH
+
+
+def load():
+    """Load (building first if the sources are newer) the CUDA library."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not os.path.exists(_build.LIB_PATH) or (_build.stale() and _build.find_nvcc()):
+        _build.build()
+    lib = C.CDLL(_build.LIB_PATH)
+    lib.ti_gemm_i8.argtypes = [C.POINTER(GemmParams)]
+    lib.ti_gemm_i8.restype = C.c_int
+    lib.ti_layernorm.argtypes = [C.POINTER(LayerNormParams)]
+    lib.ti_layernorm.restype = C.c_int
+    lib.ti_gelu_q.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_float, C.c_int32, C.c_void_p]
+    lib.ti_gelu_q.restype = C.c_int
+    lib.ti_softmax_q.argtypes = [C.c_void_p, C.c_void_p] + [C.c_int64] * 7 + [C.c_int32, C.c_float, C.c_int32, C.c_void_p]
+    lib.ti_softmax_q.restype = C.c_int
+    lib.ti_device_status.argtypes = [C.POINTER(C.c_uint32)]
+    lib.ti_device_status.restype = C.c_int
+    lib.ti_version.restype = C.c_int
+    lib.ti_last_error_string.restype = C.c_char_p
+    lib.ti_launch_count.restype = C.c_int64
+    lib.ti_device_supported.restype = C.c_int
+    _LIB = lib
+    return lib
+
+
+def check(rc: int, what: str):
+    """Map a ti_status to the exception type the reference raises for that class of error."""
+    if rc == TI_OK:
+        return
+    msg = f"{what}: {load().ti_last_error_string().decode()} (ti_status {rc})"
+    if rc == TI_ERR_SHAPE:
+        raise AssertionError(msg)  # the reference's wrappers assert on shape mismatches
+    raise RuntimeError(msg)
+
+
+def device_status() -> int:
+    st = C.c_uint32(0)
+    rc = load().ti_device_status(C.byref(st))
+    if rc not in (TI_OK, TI_ERR_TIMEOUT):
+        check(rc, "ti_device_status")
+    return st.value
+
+
+def launch_count() -> int:
+    return int(load().ti_launch_count())
+
+
+def require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("triton_int_b200 has no CPU path: all tensors must live on a CUDA device")
+
+
+def current_stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream

@@ -1,0 +1,521 @@
+// int8 x int8 -> int32 GEMM / batched GEMM for sm_100a.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer: 128B-swizzled tiles of A [BM x 128 B] and B [BN x 128 B]
+//               into a ring of shared-memory stages (plain per-CTA tensor loads)
+//   warp 1      allocates TMEM, then one lane issues tcgen05.mma kind::i8
+//               (M=128, N=BN, K=32 per instruction, 4 per stage) into one of two
+//               TMEM accumulator buffers and commits stage/accumulator barriers
+//   warps 2..5  epilogue: tcgen05.ld the int32 accumulator (each warp owns the 32
+//               TMEM lanes of its quarter), apply the fused fp32 epilogue and store
+// Every mbarrier wait is bounded; on expiry the kernel records a status bit,
+// drains and returns instead of hanging.
+#pragma once
+
+#include <cuda.h>
+
+#include "ti_common.cuh"
+
+namespace ti {
+namespace tc {
+
+constexpr int BM = 128;          // rows of A per tile = TMEM lanes
+constexpr int BK = 128;          // bytes of K per stage = one 128B swizzle row
+constexpr int UMMA_K = 32;       // K per tcgen05.mma kind::i8
+constexpr int NUM_THREADS = 192; // 6 warps
+constexpr int NUM_EPI_THREADS = 128;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+
+struct Params {
+  void* c;
+  const void* bias;
+  const float* alpha;
+  const float* beta;
+  int64_t c_stride_m, c_stride_n, c_stride_batch;
+  int m, n, k, batch;
+  int tiles_m, tiles_n, num_tiles, num_kb;
+  int bias_dtype, epilogue, rounding, causal;
+  int c_vec_ok;  // c_stride_n == 1 and rows start on 16-byte boundaries
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the limit expired or another role already
+// gave up (abort flag in shared memory).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 255u) == 0u) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major, 128B-swizzled shared-memory operand descriptor: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);   // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                     // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;           // stride byte offset
+  d |= (uint64_t)1 << 46;                     // version
+  d |= (uint64_t)2 << 61;                     // SWIZZLE_128B
+  return d;
+}
+// kind::i8 instruction descriptor: D = s32, A = B = signed int8, both K-major.
+__host__ __device__ constexpr uint32_t make_idesc_i8(int m, int n) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ------------------------------------------------------------------ tile schedule
+struct Tile {
+  int batch, m_blk, n_blk;
+};
+constexpr int GROUP_M = 8;
+__device__ __forceinline__ Tile decode_tile(int t, int tiles_m, int tiles_n) {
+  Tile r;
+  const int per_batch = tiles_m * tiles_n;
+  r.batch = t / per_batch;
+  int i = t - r.batch * per_batch;
+  const int per_group = GROUP_M * tiles_n;
+  const int group = i / per_group;
+  const int first_m = group * GROUP_M;
+  const int gsize = min(tiles_m - first_m, GROUP_M);
+  const int j = i - group * per_group;
+  r.m_blk = first_m + (j % gsize);
+  r.n_blk = j / gsize;
+  return r;
+}
+// Output tiles a causal consumer never reads: every column lies right of the
+// diagonal of every row in the tile.
+template <int BN>
+__device__ __forceinline__ bool tile_skipped(const Params& p, const Tile& t) {
+  if (!p.causal) return false;
+  const int row_last = min(t.m_blk * BM + BM - 1, p.m - 1);
+  return t.n_blk * BN > row_last + (p.n - p.m);
+}
+
+// ------------------------------------------------------------------ shared memory
+template <int BN, int STAGES>
+struct Smem {
+  static constexpr int A_BYTES = BM * BK;
+  static constexpr int B_BYTES = BN * BK;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+  // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]; then tmem base, abort flag
+  static constexpr int BAR_OFFSET = TILE_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16;
+  static constexpr int DYN_BYTES = TOTAL + 1024;  // slack to align the base to 1024
+};
+
+// ------------------------------------------------------------------ epilogue
+template <typename OutT>
+__device__ __forceinline__ void store_row32(OutT* dst, const OutT (&v)[32], int ncols, bool vec_ok, int64_t stride_n) {
+  if (vec_ok && ncols == 32) {
+    constexpr int PER16 = 16 / (int)sizeof(OutT);
+    const uint4* src = reinterpret_cast<const uint4*>(v);
+    uint4* d = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int i = 0; i < 32 / PER16; ++i) d[i] = src[i];
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) dst[(int64_t)j * stride_n] = v[j];
+  }
+}
+
+template <int BN, int STAGES, typename OutT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const Params p) {
+  using S = Smem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + S::BAR_OFFSET;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + S::BAR_OFFSET + S::NUM_BARS * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + S::BAR_OFFSET + S::NUM_BARS * 8 + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), NUM_EPI_THREADS);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32((const void*)tmem_holder), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+        const Tile tile = decode_tile(t, p.tiles_m, p.tiles_n);
+        if (tile_skipped<BN>(p, tile)) continue;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            atomicOr(&g_status, STATUS_PRODUCER);
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + stage * S::STAGE_BYTES;
+          const uint32_t b_dst = a_dst + S::A_BYTES;
+          mbar_expect_tx(full_bar(stage), S::STAGE_BYTES);
+          tma_load_3d(a_dst, &map_a, full_bar(stage), kb * BK, tile.m_blk * BM, tile.batch);
+          tma_load_3d(b_dst, &map_b, full_bar(stage), kb * BK, tile.n_blk * BN, tile.batch);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_i8(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+        const Tile tile = decode_tile(t, p.tiles_m, p.tiles_n);
+        if (tile_skipped<BN>(p, tile)) continue;
+        const int buf = local & 1;
+        const uint32_t use = (uint32_t)(local >> 1);
+        // wait until the epilogue has drained this accumulator buffer
+        if (!mbar_wait(acc_empty_bar(buf), (use & 1u) ^ 1u, abort_flag)) {
+          atomicOr(&g_status, STATUS_MMA);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+            atomicOr(&g_status, STATUS_MMA);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_src = smem_base + stage * S::STAGE_BYTES;
+          const uint32_t b_src = a_src + S::A_BYTES;
+          const uint64_t adesc = make_smem_desc(a_src);
+          const uint64_t bdesc = make_smem_desc(b_src);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advance 32 bytes of K inside the 128-byte swizzle row: +2 in 16-byte units
+            umma_i8(tmem_d, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                    (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // the stage may be refilled once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(acc_full_bar(buf));
+        ++local;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+    const float alpha = p.alpha ? *p.alpha : 1.0f;
+    const float beta = p.beta ? *p.beta : 1.0f;
+    int local = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+      const Tile tile = decode_tile(t, p.tiles_m, p.tiles_n);
+      if (tile_skipped<BN>(p, tile)) continue;
+      const int buf = local & 1;
+      const uint32_t use = (uint32_t)(local >> 1);
+      if (!mbar_wait(acc_full_bar(buf), use & 1u, abort_flag)) {
+        if (lane == 0) atomicOr(&g_status, STATUS_EPILOGUE);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row = tile.m_blk * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.m;
+      const int col0 = tile.n_blk * BN;
+      OutT* c_row = reinterpret_cast<OutT*>(p.c) + (int64_t)tile.batch * p.c_stride_batch + (int64_t)row * p.c_stride_m;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+#pragma unroll 1
+      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+        const int col = col0 + chunk * 32;
+        if (col >= p.n) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld32(taddr + (uint32_t)(chunk * 32), r);
+        tmem_ld_wait();
+        const int ncols = min(32, p.n - col);
+        alignas(16) OutT v[32];
+        if (p.epilogue == TI_EPI_I32) {
+          if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              int32_t a = (int32_t)r[j];
+              if (p.bias != nullptr && j < ncols) a += ((const int32_t*)p.bias)[col + j];
+              reinterpret_cast<int32_t*>(v)[j] = a;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float b = 0.f;
+            if (p.bias != nullptr && j < ncols) b = load_bias_f32(p.bias, p.bias_dtype, col + j);
+            float f = epilogue_f32((int32_t)r[j], b, alpha, beta, p.epilogue);
+            OutT o = OutCast<OutT>::from(f, p.rounding);
+            if constexpr (sizeof(OutT) == 1) {
+              if (p.epilogue == TI_EPI_SCALE_BIAS_RELU) o = o < 0 ? (OutT)0 : o;
+            }
+            v[j] = o;
+          }
+        }
+        if (row_ok) store_row32<OutT>(c_row + (int64_t)col * p.c_stride_n, v, ncols, p.c_vec_ok != 0, p.c_stride_n);
+      }
+      tc_fence_before();
+      mbar_arrive(acc_empty_bar(buf));
+      ++local;
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncthreads();
+  if (*abort_flag) {
+    // let loads already in flight land before the shared memory is released
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// Tensor map over an int8 operand viewed as [batch][rows][k] with k contiguous.
+inline int make_operand_map(CUtensorMap* map, const void* base, int64_t k, int64_t rows, int64_t batch,
+                            int64_t row_stride, int64_t batch_stride, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return TI_ERR_CUDA;
+  }
+  cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)row_stride, (cuuint64_t)(batch > 1 ? batch_stride : row_stride * rows)};
+  if (strides[1] == 0 || (strides[1] % 16) != 0) strides[1] = 16;  // single batch: never used to address
+  cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (k=%lld rows=%lld batch=%lld row_stride=%lld)", (int)r,
+              (long long)k, (long long)rows, (long long)batch, (long long)row_stride);
+    return TI_ERR_CUDA;
+  }
+  return TI_OK;
+}
+
+// True when the tensor-map path can address this problem: both operands K-contiguous,
+// 16-byte aligned bases and 16-byte multiple row/batch strides.
+inline bool eligible(const ti_gemm_params& g) {
+  if (g.m <= 0 || g.n <= 0 || g.k <= 0 || g.batch <= 0) return false;
+  if (g.a_stride_k != 1 || g.b_stride_k != 1) return false;
+  if (((uintptr_t)g.a & 15) || ((uintptr_t)g.b & 15)) return false;
+  if ((g.a_stride_m % 16) || (g.b_stride_n % 16)) return false;
+  if (g.a_stride_m < g.k || g.b_stride_n < g.k) return false;
+  if (g.batch > 1 && ((g.a_stride_batch % 16) || (g.b_stride_batch % 16))) return false;
+  if (g.batch > 1 && (g.a_stride_batch <= 0 || g.b_stride_batch <= 0)) return false;
+  if (g.m >= (1ll << 31) || g.n >= (1ll << 31) || g.k >= (1ll << 31) || g.batch >= (1ll << 31)) return false;
+  return true;
+}
+
+template <int BN, int STAGES, typename OutT>
+int launch_cfg(const ti_gemm_params& g, int num_sms) {
+  using S = Smem<BN, STAGES>;
+  CUtensorMap map_a, map_b;
+  int rc = make_operand_map(&map_a, g.a, g.k, g.m, g.batch, g.a_stride_m, g.a_stride_batch, BM);
+  if (rc != TI_OK) return rc;
+  rc = make_operand_map(&map_b, g.b, g.k, g.n, g.batch, g.b_stride_n, g.b_stride_batch, BN);
+  if (rc != TI_OK) return rc;
+
+  Params p;
+  p.c = g.c;
+  p.bias = g.bias;
+  p.alpha = g.alpha;
+  p.beta = g.beta;
+  p.c_stride_m = g.c_stride_m;
+  p.c_stride_n = g.c_stride_n;
+  p.c_stride_batch = g.c_stride_batch;
+  p.m = (int)g.m; p.n = (int)g.n; p.k = (int)g.k; p.batch = (int)g.batch;
+  p.tiles_m = (int)((g.m + BM - 1) / BM);
+  p.tiles_n = (int)((g.n + BN - 1) / BN);
+  const int64_t nt = (int64_t)p.tiles_m * p.tiles_n * g.batch;
+  if (nt >= (1ll << 31)) { set_error("too many tiles"); return TI_ERR_SHAPE; }
+  p.num_tiles = (int)nt;
+  p.num_kb = (int)((g.k + BK - 1) / BK);
+  p.bias_dtype = g.bias_dtype;
+  p.epilogue = g.epilogue;
+  p.rounding = g.rounding;
+  p.causal = g.causal;
+  const int64_t esz = (int64_t)sizeof(OutT);
+  p.c_vec_ok = (g.c_stride_n == 1) && (((uintptr_t)g.c & 15) == 0) && ((g.c_stride_m * esz) % 16 == 0) &&
+               ((g.c_stride_batch * esz) % 16 == 0);
+
+  auto kern = gemm_i8_tcgen05_kernel<BN, STAGES, OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    TI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::DYN_BYTES));
+    attr_set = true;
+  }
+  const int grid = p.num_tiles < num_sms ? p.num_tiles : num_sms;
+  kern<<<grid, NUM_THREADS, S::DYN_BYTES, (cudaStream_t)g.stream>>>(map_a, map_b, p);
+  count_launch();
+  TI_CUDA_CHECK(cudaGetLastError());
+  return TI_OK;
+}
+
+template <typename OutT>
+int launch_out(const ti_gemm_params& g, int num_sms) {
+  // 128x256 tiles when N is wide enough to fill them, else 128x128 / 128x64
+  if (g.n > 128) return launch_cfg<256, 4, OutT>(g, num_sms);
+  if (g.n > 64) return launch_cfg<128, 6, OutT>(g, num_sms);
+  return launch_cfg<64, 8, OutT>(g, num_sms);
+}
+
+inline int launch(const ti_gemm_params& g, int num_sms) {
+  switch (g.out_dtype) {
+    case TI_I8: return launch_out<int8_t>(g, num_sms);
+    case TI_I32: return launch_out<int32_t>(g, num_sms);
+    case TI_F32: return launch_out<float>(g, num_sms);
+    case TI_F16: return launch_out<__half>(g, num_sms);
+    case TI_BF16: return launch_out<__nv_bfloat16>(g, num_sms);
+  }
+  set_error("unsupported output dtype %d", g.out_dtype);
+  return TI_ERR_DTYPE;
+}
+
+}  // namespace tc
+}  // namespace ti

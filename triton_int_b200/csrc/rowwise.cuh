@@ -1,0 +1,514 @@
+// Memory-bound row kernels: the LayerNorm family (with optional int32 dequant +
+// residual add in front and int8 quantisation behind), the stand-alone int8 GELU
+// and the causal softmax -> int8 step between the two attention BMMs.
+// All of them read each input byte once with 16-byte (or 8-byte) vector loads,
+// keep the row in registers, reduce with warp shuffles + one shared-memory hop,
+// and write each output byte once.
+#pragma once
+
+#include <type_traits>
+
+#include "ti_common.cuh"
+
+namespace ti {
+namespace row {
+
+// ------------------------------------------------------------------ reductions
+// A row is owned by `tpr` consecutive threads (a multiple of 32) of the CTA.
+template <bool IS_MAX>
+__device__ __forceinline__ float row_reduce(float v, int tpr, int tid_in_row, int row_in_cta, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = IS_MAX ? fmaxf(v, other) : v + other;
+  }
+  if (tpr == 32) return v;
+  const int warps = tpr >> 5;
+  float* r = red + row_in_cta * 32;
+  __syncthreads();  // previous use of `red` is over
+  if ((tid_in_row & 31) == 0) r[tid_in_row >> 5] = v;
+  __syncthreads();
+  float t = r[0];
+  for (int w = 1; w < warps; ++w) t = IS_MAX ? fmaxf(t, r[w]) : t + r[w];
+  return t;
+}
+
+// ------------------------------------------------------------------ typed 4-element access
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&o)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&o)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]);
+  }
+};
+template <> struct Vec4<__half> {
+  static __device__ __forceinline__ void load(const __half* p, float (&o)[4]) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const __half2 a = *reinterpret_cast<const __half2*>(&v.x), b = *reinterpret_cast<const __half2*>(&v.y);
+    o[0] = __low2float(a); o[1] = __high2float(a); o[2] = __low2float(b); o[3] = __high2float(b);
+  }
+  static __device__ __forceinline__ void store(__half* p, const float (&o)[4]) {
+    __half2 a = __halves2half2(__float2half_rn(o[0]), __float2half_rn(o[1]));
+    __half2 b = __halves2half2(__float2half_rn(o[2]), __float2half_rn(o[3]));
+    uint2 v;
+    v.x = *reinterpret_cast<unsigned*>(&a); v.y = *reinterpret_cast<unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = v;
+  }
+};
+template <> struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&o)[4]) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    o[0] = __uint_as_float(v.x << 16); o[1] = __uint_as_float(v.x & 0xffff0000u);
+    o[2] = __uint_as_float(v.y << 16); o[3] = __uint_as_float(v.y & 0xffff0000u);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&o)[4]) {
+    __nv_bfloat16 h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __float2bfloat16_rn(o[i]);
+    *reinterpret_cast<uint2*>(p) = *reinterpret_cast<uint2*>(h);
+  }
+};
+template <> struct Vec4<int8_t> {
+  static __device__ __forceinline__ void store_q(int8_t* p, const float (&o)[4], int rounding) {
+    char4 c;
+    c.x = cast_i8(o[0], rounding); c.y = cast_i8(o[1], rounding);
+    c.z = cast_i8(o[2], rounding); c.w = cast_i8(o[3], rounding);
+    *reinterpret_cast<char4*>(p) = c;
+  }
+};
+
+// round a float to the storage type and back (the skip variants add the skip
+// tensor to the already-rounded LayerNorm output, kernels/fused.py:622-635)
+template <typename T> __device__ __forceinline__ float round_through(float f);
+template <> __device__ __forceinline__ float round_through<float>(float f) { return f; }
+template <> __device__ __forceinline__ float round_through<__half>(float f) { return __half2float(__float2half_rn(f)); }
+template <> __device__ __forceinline__ float round_through<__nv_bfloat16>(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+
+struct LnParams {
+  const void* x;
+  const float* residual_in;
+  float* residual_out;
+  const int32_t* bias_i32;
+  const void* gamma;
+  const void* beta;
+  const void* skip;
+  void* out;
+  void* out2;
+  const float* dq_scale_dev;
+  int64_t rows, n;
+  int64_t x_row_stride, x_col_stride, out_row_stride, out_col_stride;
+  float eps, dq_scale;
+  int rounding, rms;
+};
+
+// ------------------------------------------------------------------ LayerNorm, vector path
+// XT: float / half / bf16 / int32 (dequant+residual).  PT: dtype of gamma, beta, skip and
+// of a non-int8 output.  QOUT: int8 output.  MAXV float4-groups per thread.
+template <typename XT, typename PT, bool QOUT, int MAXV>
+__global__ void __launch_bounds__(512)
+layernorm_vec_kernel(const LnParams p, const int tpr) {
+  __shared__ float red[32 * 32];
+  const int rows_per_cta = blockDim.x / tpr;
+  const int row_in_cta = threadIdx.x / tpr;
+  const int tid = threadIdx.x - row_in_cta * tpr;
+  const int64_t row = (int64_t)blockIdx.x * rows_per_cta + row_in_cta;
+  const bool row_ok = row < p.rows;
+  const int n = (int)p.n;
+  float v[MAXV][4];
+
+  // ---- load (and dequantise + add the residual) ----
+  float dq = p.dq_scale;
+  if constexpr (std::is_same<XT, int32_t>::value) {
+    if (p.dq_scale_dev) dq = *p.dq_scale_dev;
+  }
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int col = (i * tpr + tid) * 4;
+    if (row_ok && col < n) {
+      if constexpr (std::is_same<XT, int32_t>::value) {
+        int4 a = *reinterpret_cast<const int4*>((const int32_t*)p.x + row * p.x_row_stride + col);
+        if (p.bias_i32) {
+          const int4 b = *reinterpret_cast<const int4*>(p.bias_i32 + col);
+          a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        const float4 r = *reinterpret_cast<const float4*>(p.residual_in + row * n + col);
+        // residual + scale * int32 as one fused multiply-add: what torch.add(residual,
+        // int32, alpha=scale) evaluates (functional/fused.py:9)
+        v[i][0] = __fmaf_rn(__int2float_rn(a.x), dq, r.x);
+        v[i][1] = __fmaf_rn(__int2float_rn(a.y), dq, r.y);
+        v[i][2] = __fmaf_rn(__int2float_rn(a.z), dq, r.z);
+        v[i][3] = __fmaf_rn(__int2float_rn(a.w), dq, r.w);
+        if (p.residual_out) Vec4<float>::store(p.residual_out + row * n + col, v[i]);
+      } else {
+        Vec4<XT>::load((const XT*)p.x + row * p.x_row_stride + col, v[i]);
+      }
+    } else {
+      v[i][0] = v[i][1] = v[i][2] = v[i][3] = 0.f;
+    }
+  }
+
+  // ---- statistics: mean, then the centred second moment, both over registers ----
+  float mean = 0.f;
+  if (!p.rms) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) s += (v[i][0] + v[i][1]) + (v[i][2] + v[i][3]);
+    s = row_reduce<false>(s, tpr, tid, row_in_cta, red);
+    mean = s / (float)n;
+  }
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int col = (i * tpr + tid) * 4;
+    if (col < n) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float d = v[i][j] - mean;
+        q += d * d;
+      }
+    }
+  }
+  q = row_reduce<false>(q, tpr, tid, row_in_cta, red);
+  const float rstd = 1.0f / sqrtf(q / (float)n + p.eps);
+
+  // ---- normalise, scale, shift, store ----
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int col = (i * tpr + tid) * 4;
+    if (!(row_ok && col < n)) continue;
+    float g[4], o[4];
+    Vec4<PT>::load((const PT*)p.gamma + col, g);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = ((v[i][j] - mean) * rstd) * g[j];
+    if (p.beta) {
+      float b[4];
+      Vec4<PT>::load((const PT*)p.beta + col, b);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[j] += b[j];
+    }
+    if constexpr (QOUT) {
+      Vec4<int8_t>::store_q((int8_t*)p.out + row * p.out_row_stride + col, o, p.rounding);
+    } else {
+      if (p.out) Vec4<PT>::store((PT*)p.out + row * p.out_row_stride + col, o);
+      if (p.out2) {
+        float s[4];
+        Vec4<PT>::load((const PT*)p.skip + row * p.x_row_stride + col, s);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[j] += round_through<PT>(o[j]);
+        Vec4<PT>::store((PT*)p.out2 + row * p.out_row_stride + col, s);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ LayerNorm, any strides / any N
+template <typename XT, typename PT, bool QOUT>
+__global__ void __launch_bounds__(256)
+layernorm_any_kernel(const LnParams p) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const int64_t n = p.n;
+  float dq = p.dq_scale;
+  if constexpr (std::is_same<XT, int32_t>::value) {
+    if (p.dq_scale_dev) dq = *p.dq_scale_dev;
+  }
+  auto load = [&](int64_t col) -> float {
+    if constexpr (std::is_same<XT, int32_t>::value) {
+      int32_t a = ((const int32_t*)p.x)[row * p.x_row_stride + col * p.x_col_stride];
+      if (p.bias_i32) a += p.bias_i32[col];
+      return __fmaf_rn(__int2float_rn(a), dq, p.residual_in[row * n + col]);
+    } else if constexpr (std::is_same<XT, float>::value) {
+      return ((const float*)p.x)[row * p.x_row_stride + col * p.x_col_stride];
+    } else if constexpr (std::is_same<XT, __half>::value) {
+      return __half2float(((const __half*)p.x)[row * p.x_row_stride + col * p.x_col_stride]);
+    } else {
+      return __bfloat162float(((const __nv_bfloat16*)p.x)[row * p.x_row_stride + col * p.x_col_stride]);
+    }
+  };
+  auto loadp = [&](const void* base, int64_t idx) -> float {
+    if constexpr (std::is_same<PT, float>::value) return ((const float*)base)[idx];
+    else if constexpr (std::is_same<PT, __half>::value) return __half2float(((const __half*)base)[idx]);
+    else return __bfloat162float(((const __nv_bfloat16*)base)[idx]);
+  };
+  float mean = 0.f;
+  if (!p.rms) {
+    float s = 0.f;
+    for (int64_t c = threadIdx.x; c < n; c += blockDim.x) s += load(c);
+    s = row_reduce<false>(s, blockDim.x, threadIdx.x, 0, red);
+    mean = s / (float)n;
+  }
+  float q = 0.f;
+  for (int64_t c = threadIdx.x; c < n; c += blockDim.x) {
+    const float d = load(c) - mean;
+    q += d * d;
+  }
+  q = row_reduce<false>(q, blockDim.x, threadIdx.x, 0, red);
+  const float rstd = 1.0f / sqrtf(q / (float)n + p.eps);
+  for (int64_t c = threadIdx.x; c < n; c += blockDim.x) {
+    const float x = load(c);
+    if constexpr (std::is_same<XT, int32_t>::value) {
+      if (p.residual_out) p.residual_out[row * n + c] = x;
+    }
+    float o = ((x - mean) * rstd) * loadp(p.gamma, c);
+    if (p.beta) o += loadp(p.beta, c);
+    const int64_t oi = row * p.out_row_stride + c * p.out_col_stride;
+    if constexpr (QOUT) {
+      ((int8_t*)p.out)[oi] = cast_i8(o, p.rounding);
+    } else {
+      if (p.out) ((PT*)p.out)[oi] = OutCast<PT>::from(o, 0);
+      if (p.out2) {
+        const float s = loadp(p.skip, row * p.x_row_stride + c * p.x_col_stride);
+        ((PT*)p.out2)[oi] = OutCast<PT>::from(round_through<PT>(o) + s, 0);
+      }
+    }
+  }
+}
+
+inline int pick_tpr(int64_t n, int* maxv) {
+  // about 16 elements per thread, 32..512 threads per row
+  int tpr = 32;
+  while (tpr < 512 && (int64_t)tpr * 16 < n) tpr <<= 1;
+  int64_t v = (n + (int64_t)tpr * 4 - 1) / ((int64_t)tpr * 4);
+  int mv = 1;
+  while (mv < v) mv <<= 1;
+  *maxv = mv;
+  return tpr;
+}
+
+template <typename XT, typename PT, bool QOUT>
+int launch_ln_typed(const ti_layernorm_params& g, const LnParams& p, bool vec_ok) {
+  cudaStream_t st = (cudaStream_t)g.stream;
+  int maxv = 0;
+  const int tpr = pick_tpr(g.n, &maxv);
+  if (vec_ok && maxv <= 16) {
+    const int threads = tpr < 128 ? 128 : tpr;
+    const int rows_per_cta = threads / tpr;
+    const int64_t grid = (g.rows + rows_per_cta - 1) / rows_per_cta;
+    if (grid >= (1ll << 31)) { set_error("too many rows"); return TI_ERR_SHAPE; }
+    switch (maxv) {
+      case 1: layernorm_vec_kernel<XT, PT, QOUT, 1><<<(unsigned)grid, threads, 0, st>>>(p, tpr); break;
+      case 2: layernorm_vec_kernel<XT, PT, QOUT, 2><<<(unsigned)grid, threads, 0, st>>>(p, tpr); break;
+      case 4: layernorm_vec_kernel<XT, PT, QOUT, 4><<<(unsigned)grid, threads, 0, st>>>(p, tpr); break;
+      case 8: layernorm_vec_kernel<XT, PT, QOUT, 8><<<(unsigned)grid, threads, 0, st>>>(p, tpr); break;
+      default: layernorm_vec_kernel<XT, PT, QOUT, 16><<<(unsigned)grid, threads, 0, st>>>(p, tpr); break;
+    }
+  } else {
+    if (g.rows >= (1ll << 31)) { set_error("too many rows"); return TI_ERR_SHAPE; }
+    layernorm_any_kernel<XT, PT, QOUT><<<(unsigned)g.rows, 256, 0, st>>>(p);
+  }
+  count_launch();
+  TI_CUDA_CHECK(cudaGetLastError());
+  return TI_OK;
+}
+
+inline bool aligned(const void* p, int a) { return p == nullptr || ((uintptr_t)p % a) == 0; }
+
+inline int launch_layernorm(const ti_layernorm_params& g) {
+  if (g.rows < 0 || g.n <= 0) { set_error("layernorm: bad extents rows=%lld n=%lld", (long long)g.rows, (long long)g.n); return TI_ERR_SHAPE; }
+  if (g.rows == 0) return TI_OK;
+  if (!g.x || !g.gamma || (!g.out && !g.out2)) { set_error("layernorm: null pointer"); return TI_ERR_DEVICE; }
+  const bool is_dq = g.x_dtype == TI_I32;
+  if (is_dq && !g.residual_in) { set_error("layernorm: int32 input needs residual_in"); return TI_ERR_DEVICE; }
+  if (g.out2 && !g.skip) { set_error("layernorm: out2 needs skip"); return TI_ERR_DEVICE; }
+  const bool qout = g.out_dtype == TI_I8;
+  if (qout && (g.out2 || !g.out)) { set_error("layernorm: int8 output has no skip variant"); return TI_ERR_UNSUPPORTED; }
+  if (!qout && g.out_dtype != g.param_dtype) { set_error("layernorm: float output dtype must equal the parameter dtype"); return TI_ERR_DTYPE; }
+  if (!is_dq && g.x_dtype != g.param_dtype) { set_error("layernorm: input and parameter dtypes differ"); return TI_ERR_DTYPE; }
+  if (is_dq && g.param_dtype != TI_F32) { set_error("layernorm: dequantising path needs fp32 parameters"); return TI_ERR_DTYPE; }
+
+  LnParams p;
+  p.x = g.x; p.residual_in = g.residual_in; p.residual_out = g.residual_out; p.bias_i32 = g.bias_i32;
+  p.gamma = g.gamma; p.beta = g.beta; p.skip = g.skip; p.out = g.out; p.out2 = g.out2;
+  p.dq_scale_dev = g.dq_scale_dev;
+  p.rows = g.rows; p.n = g.n;
+  p.x_row_stride = g.x_row_stride; p.x_col_stride = g.x_col_stride;
+  p.out_row_stride = g.out_row_stride; p.out_col_stride = g.out_col_stride;
+  p.eps = g.eps; p.dq_scale = g.dq_scale; p.rounding = g.rounding; p.rms = g.rms;
+
+  const int xs = dtype_size(g.x_dtype), ps = dtype_size(g.param_dtype), os = dtype_size(g.out_dtype);
+  if (!xs || !ps || !os) { set_error("layernorm: bad dtype"); return TI_ERR_DTYPE; }
+  bool vec_ok = (g.n % 4 == 0) && g.x_col_stride == 1 && g.out_col_stride == 1 &&
+                aligned(g.x, 4 * xs) && (g.x_row_stride * xs) % (4 * xs) == 0 &&
+                aligned(g.out, 4 * os) && aligned(g.out2, 4 * os) && (g.out_row_stride * os) % (4 * os) == 0 &&
+                aligned(g.gamma, 4 * ps) && aligned(g.beta, 4 * ps) && aligned(g.skip, 4 * ps) &&
+                aligned(g.residual_in, 16) && aligned(g.residual_out, 16) && aligned(g.bias_i32, 16);
+
+#define TI_LN_DISPATCH(XT, PT)                                                   \
+  return qout ? launch_ln_typed<XT, PT, true>(g, p, vec_ok) : launch_ln_typed<XT, PT, false>(g, p, vec_ok)
+  if (is_dq) { TI_LN_DISPATCH(int32_t, float); }
+  switch (g.param_dtype) {
+    case TI_F32: TI_LN_DISPATCH(float, float);
+    case TI_F16: TI_LN_DISPATCH(__half, __half);
+    case TI_BF16: TI_LN_DISPATCH(__nv_bfloat16, __nv_bfloat16);
+  }
+#undef TI_LN_DISPATCH
+  set_error("layernorm: unsupported parameter dtype %d", g.param_dtype);
+  return TI_ERR_DTYPE;
+}
+
+// ------------------------------------------------------------------ int8 GELU
+// Only 256 distinct inputs exist, so each CTA tabulates the function once
+// (accurate tanhf) and then streams: 16 bytes in, 16 look-ups, 16 bytes out.
+// The table is replicated per lane (entry = value*32 + lane) so that the 32
+// look-ups of a warp never collide on a shared-memory bank.
+__global__ void __launch_bounds__(256)
+gelu_q_kernel(const int8_t* __restrict__ x, int8_t* __restrict__ y, int64_t n, float in_scale, float out_mul,
+              int rounding, int vec_ok) {
+  __shared__ uint32_t lut[256 * 32];
+  {
+    const int val = (int)(int8_t)threadIdx.x;  // blockDim.x == 256: one input value per thread
+    const float f = gelu_tanh_scaled(__fmul_rn((float)val, in_scale), out_mul);
+    const uint32_t q = (uint32_t)(uint8_t)cast_i8(f, rounding);
+#pragma unroll 8
+    for (int l = 0; l < 32; ++l) lut[threadIdx.x * 32 + l] = q;
+  }
+  __syncthreads();
+  const uint32_t* my = lut + (threadIdx.x & 31);
+  auto look = [&](uint32_t byte) -> uint32_t { return my[byte << 5]; };
+  auto word = [&](uint32_t w) -> uint32_t {
+    return look(w & 0xffu) | (look((w >> 8) & 0xffu) << 8) | (look((w >> 16) & 0xffu) << 16) | (look(w >> 24) << 24);
+  };
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t gtid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (vec_ok) {
+    const int64_t nvec = n >> 4;
+    const uint4* xv = reinterpret_cast<const uint4*>(x);
+    uint4* yv = reinterpret_cast<uint4*>(y);
+    for (int64_t i = gtid; i < nvec; i += stride) {
+      uint4 v = __ldcs(xv + i);
+      v.x = word(v.x); v.y = word(v.y); v.z = word(v.z); v.w = word(v.w);
+      __stcs(yv + i, v);
+    }
+    for (int64_t i = (nvec << 4) + gtid; i < n; i += stride) y[i] = (int8_t)look((uint8_t)x[i]);
+  } else {
+    for (int64_t i = gtid; i < n; i += stride) y[i] = (int8_t)look((uint8_t)x[i]);
+  }
+}
+
+inline int launch_gelu_q(const int8_t* x, int8_t* y, int64_t n, float in_scale, float out_mul, int rounding,
+                         void* stream, int num_sms) {
+  if (n < 0) { set_error("gelu_q: negative size"); return TI_ERR_SHAPE; }
+  if (n == 0) return TI_OK;
+  if (!x || !y) { set_error("gelu_q: null pointer"); return TI_ERR_DEVICE; }
+  const int vec_ok = (((uintptr_t)x | (uintptr_t)y) & 15) == 0;
+  int64_t want = (n / 16 + 255) / 256;
+  int64_t cap = (int64_t)num_sms * 8;
+  int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+  gelu_q_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(x, y, n, in_scale, out_mul, rounding, vec_ok);
+  count_launch();
+  TI_CUDA_CHECK(cudaGetLastError());
+  return TI_OK;
+}
+
+// ------------------------------------------------------------------ causal softmax -> int8
+struct SmParams {
+  const float* s;
+  int8_t* p;
+  int64_t batch, m, n;
+  int64_t s_row_stride, s_batch_stride, p_row_stride, p_batch_stride;
+  float out_mul;
+  int causal, rounding;
+};
+
+template <int MAXV, bool VEC>
+__global__ void __launch_bounds__(512)
+softmax_q_kernel(const SmParams p, const int tpr) {
+  __shared__ float red[32 * 32];
+  const int rows_per_cta = blockDim.x / tpr;
+  const int row_in_cta = threadIdx.x / tpr;
+  const int tid = threadIdx.x - row_in_cta * tpr;
+  const int64_t grow = (int64_t)blockIdx.x * rows_per_cta + row_in_cta;  // over batch*m
+  const bool row_ok = grow < p.batch * p.m;
+  const int64_t b = row_ok ? grow / p.m : 0;
+  const int64_t i = row_ok ? grow - b * p.m : 0;
+  const int n = (int)p.n;
+  // number of visible keys of this query row
+  int64_t vis64 = p.causal ? (i + (p.n - p.m) + 1) : p.n;
+  const int vis = (int)(vis64 < 0 ? 0 : (vis64 > p.n ? p.n : vis64));
+  const float* srow = p.s + b * p.s_batch_stride + i * p.s_row_stride;
+  int8_t* prow = p.p + b * p.p_batch_stride + i * p.p_row_stride;
+  const float NEG_INF = __int_as_float(0xff800000);
+
+  float v[MAXV][4];
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k) {
+    const int col = (k * tpr + tid) * 4;
+    v[k][0] = v[k][1] = v[k][2] = v[k][3] = NEG_INF;
+    if (row_ok && col < vis) {
+      if (VEC && col + 4 <= n) {
+        Vec4<float>::load(srow + col, v[k]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) if (col + j < n) v[k][j] = srow[col + j];
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) if (col + j >= vis) v[k][j] = NEG_INF;
+    }
+  }
+  float mx = NEG_INF;
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k) mx = fmaxf(mx, fmaxf(fmaxf(v[k][0], v[k][1]), fmaxf(v[k][2], v[k][3])));
+  mx = row_reduce<true>(mx, tpr, tid, row_in_cta, red);
+  float sum = 0.f;
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float e = (v[k][j] == NEG_INF) ? 0.f : expf(v[k][j] - mx);
+      v[k][j] = e;
+      sum += e;
+    }
+  }
+  sum = row_reduce<false>(sum, tpr, tid, row_in_cta, red);
+  const float inv = (vis > 0) ? 1.0f / sum : 0.f;
+#pragma unroll
+  for (int k = 0; k < MAXV; ++k) {
+    const int col = (k * tpr + tid) * 4;
+    if (!(row_ok && col < n)) continue;
+    float o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = (v[k][j] * inv) * p.out_mul;
+    if (VEC && col + 4 <= n) {
+      Vec4<int8_t>::store_q(prow + col, o, p.rounding);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) if (col + j < n) prow[col + j] = cast_i8(o[j], p.rounding);
+    }
+  }
+}
+
+inline int launch_softmax_q(const SmParams& p, void* stream) {
+  if (p.batch < 0 || p.m < 0 || p.n <= 0) { set_error("softmax_q: bad extents"); return TI_ERR_SHAPE; }
+  if (p.batch == 0 || p.m == 0) return TI_OK;
+  if (!p.s || !p.p) { set_error("softmax_q: null pointer"); return TI_ERR_DEVICE; }
+  int maxv = 0;
+  const int tpr = pick_tpr(p.n, &maxv);
+  if (maxv > 16) { set_error("softmax_q: rows longer than 32768 are not supported"); return TI_ERR_UNSUPPORTED; }
+  const bool vec = (((uintptr_t)p.s & 15) == 0) && (p.s_row_stride % 4 == 0) && (p.s_batch_stride % 4 == 0) &&
+                   (((uintptr_t)p.p & 3) == 0) && (p.p_row_stride % 4 == 0) && (p.p_batch_stride % 4 == 0);
+  const int threads = tpr < 128 ? 128 : tpr;
+  const int rows_per_cta = threads / tpr;
+  const int64_t grid = (p.batch * p.m + rows_per_cta - 1) / rows_per_cta;
+  if (grid >= (1ll << 31)) { set_error("softmax_q: too many rows"); return TI_ERR_SHAPE; }
+  cudaStream_t st = (cudaStream_t)stream;
+#define TI_SM_LAUNCH(MV)                                                                  \
+  if (vec) softmax_q_kernel<MV, true><<<(unsigned)grid, threads, 0, st>>>(p, tpr);        \
+  else softmax_q_kernel<MV, false><<<(unsigned)grid, threads, 0, st>>>(p, tpr)
+  switch (maxv) {
+    case 1: TI_SM_LAUNCH(1); break;
+    case 2: TI_SM_LAUNCH(2); break;
+    case 4: TI_SM_LAUNCH(4); break;
+    case 8: TI_SM_LAUNCH(8); break;
+    default: TI_SM_LAUNCH(16); break;
+  }
+#undef TI_SM_LAUNCH
+  count_launch();
+  TI_CUDA_CHECK(cudaGetLastError());
+  return TI_OK;
+}
+
+}  // namespace row
+}  // namespace ti
