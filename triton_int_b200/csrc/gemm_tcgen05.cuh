@@ -7,12 +7,16 @@
 //               (M=128, N=BN, K=32 per instruction, 4 per stage) into one of two
 //               TMEM accumulator buffers and commits stage/accumulator barriers
 //   warps 2..5  epilogue: tcgen05.ld the int32 accumulator (each warp owns the 32
-//               TMEM lanes of its quarter), apply the fused fp32 epilogue and store
+//               TMEM lanes of its quarter), apply the fused fp32 epilogue, stage
+//               128-byte output rows in swizzled shared memory and write them
+//               with TMA tensor stores (which clip ragged edges); outputs TMA
+//               cannot address fall back to per-row vector/scalar stores
 // Every mbarrier wait is bounded; on expiry the kernel records a status bit,
 // drains and returns instead of hanging.
 #pragma once
 
 #include <cuda.h>
+#include <cstring>
 
 #include "ti_common.cuh"
 
@@ -36,6 +40,7 @@ struct Params {
   int tiles_m, tiles_n, num_tiles, num_kb;
   int bias_dtype, epilogue, rounding, causal;
   int c_vec_ok;  // c_stride_n == 1 and rows start on 16-byte boundaries
+  int c_tma_ok;  // map_c is valid: output written with tensor stores
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -91,6 +96,23 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       " [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+      ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
@@ -186,11 +208,20 @@ struct Smem {
   static constexpr int B_BYTES = BN * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
-  // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]; then tmem base, abort flag
-  static constexpr int BAR_OFFSET = TILE_BYTES;
-  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  // output staging: 4 epilogue warps x 2 buffers x (32 rows x 128 bytes)
+  static constexpr int OUT_BUF_BYTES = 32 * 128;
+  static constexpr int OUT_OFFSET = TILE_BYTES;
+  static constexpr int OUT_BYTES = 4 * 2 * OUT_BUF_BYTES;
+  // per-tile bias row (fp32 or raw int32 bits)
+  static constexpr int BIAS_OFFSET = OUT_OFFSET + OUT_BYTES;
+  static constexpr int BIAS_BYTES = BN * 4;
+  // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], bias_ready, bias_free;
+  // then tmem base, abort flag
+  static constexpr int BAR_OFFSET = BIAS_OFFSET + BIAS_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 6;
   static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;  // slack to align the base to 1024
+  static_assert(DYN_BYTES <= 232448, "exceeds the 227 KB shared memory of one CTA");
 };
 
 // ------------------------------------------------------------------ epilogue
@@ -209,10 +240,60 @@ __device__ __forceinline__ void store_row32(OutT* dst, const OutT (&v)[32], int 
   }
 }
 
+// 32 accumulators of one row -> 32 outputs.  `bias_c` points at this chunk's 32
+// staged bias values in shared memory (already multiplied by beta for the
+// scale+bias epilogues; raw int32 bits for the int32 epilogue) or is null.
+template <typename OutT>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const float* bias_c, float alpha, float beta,
+                                               int epilogue, int rounding, OutT (&v)[32]) {
+  switch (epilogue) {
+    case TI_EPI_I32:
+      if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          int32_t a = (int32_t)r[j];
+          if (bias_c) a += __float_as_int(bias_c[j]);
+          reinterpret_cast<int32_t*>(v)[j] = a;
+        }
+      }
+      break;
+    case TI_EPI_SCALE:
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        v[j] = OutCast<OutT>::from(__fmul_rn(__int2float_rn((int32_t)r[j]), alpha), rounding);
+      break;
+    case TI_EPI_SCALE_BIAS:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float b = bias_c ? bias_c[j] : 0.f;
+        v[j] = OutCast<OutT>::from(__fadd_rn(b, __fmul_rn(__int2float_rn((int32_t)r[j]), alpha)), rounding);
+      }
+      break;
+    case TI_EPI_SCALE_BIAS_RELU:
+      if constexpr (sizeof(OutT) == 1) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float b = bias_c ? bias_c[j] : 0.f;
+          const OutT o = OutCast<OutT>::from(__fadd_rn(b, __fmul_rn(__int2float_rn((int32_t)r[j]), alpha)), rounding);
+          v[j] = o < 0 ? (OutT)0 : o;  // ReLU after the int8 cast, as the reference orders it
+        }
+      }
+      break;
+    case TI_EPI_GELU_Q:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float b = bias_c ? bias_c[j] : 0.f;
+        const float x = __fadd_rn(__fmul_rn(__int2float_rn((int32_t)r[j]), alpha), b);
+        v[j] = OutCast<OutT>::from(gelu_tanh_scaled(x, beta), rounding);
+      }
+      break;
+  }
+}
+
 template <int BN, int STAGES, typename OutT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                       const Params p) {
+                       const __grid_constant__ CUtensorMap map_c, const Params p) {
   using S = Smem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -222,6 +303,8 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  const uint32_t bias_ready_bar = bar_base + 8u * (2 * STAGES + 4);
+  const uint32_t bias_free_bar = bar_base + 8u * (2 * STAGES + 5);
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + S::BAR_OFFSET + S::NUM_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + S::BAR_OFFSET + S::NUM_BARS * 8 + 4);
 
@@ -238,6 +321,8 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       mbar_init(acc_full_bar(b), 1);
       mbar_init(acc_empty_bar(b), NUM_EPI_THREADS);
     }
+    mbar_init(bias_ready_bar, NUM_EPI_THREADS);
+    mbar_init(bias_free_bar, NUM_EPI_THREADS);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -323,8 +408,21 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   } else {
     // ------------------------------------------------------------ epilogue warps
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+    const int epi_tid = threadIdx.x - 64;
     const float alpha = p.alpha ? *p.alpha : 1.0f;
     const float beta = p.beta ? *p.beta : 1.0f;
+    constexpr int ESZ = (int)sizeof(OutT);
+    constexpr int ROW_BYTES = (BN * ESZ < 128) ? BN * ESZ : 128;  // one staged output row
+    constexpr int COLS_PER_BUF = ROW_BYTES / ESZ;
+    constexpr int CHUNKS_PER_BUF = COLS_PER_BUF / 32;
+    constexpr bool SWZ = (ROW_BYTES == 128);
+    constexpr int NV = 32 * ESZ / 16;  // 16-byte pieces per 32-column chunk
+    constexpr int NCHUNK = BN / 32;
+    static_assert(CHUNKS_PER_BUF >= 1 && NCHUNK % 2 == 0, "tile width");
+    float* bias_s = reinterpret_cast<float*>(smem + S::BIAS_OFFSET);
+    const uint32_t stage_base = smem_base + S::OUT_OFFSET + (uint32_t)((warp - 2) * 2 * S::OUT_BUF_BYTES);
+    const bool has_bias = p.bias != nullptr;
+    int out_buf = 0;
     int local = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
@@ -332,54 +430,102 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       if (tile_skipped<BN>(p, tile)) continue;
       const int buf = local & 1;
       const uint32_t use = (uint32_t)(local >> 1);
+      const int col0 = tile.n_blk * BN;
+      if (has_bias) {
+        // stage this tile's bias row once the previous tile's readers are done
+        if (!mbar_wait(bias_free_bar, ((uint32_t)local & 1u) ^ 1u, abort_flag)) {
+          if (lane == 0) atomicOr(&g_status, STATUS_EPILOGUE);
+          ok = false;
+          break;
+        }
+        for (int c = epi_tid; c < BN; c += NUM_EPI_THREADS) {
+          const int col = col0 + c;
+          float bv = 0.f;
+          if (col < p.n) {
+            if (p.epilogue == TI_EPI_I32) {
+              bv = __int_as_float(((const int32_t*)p.bias)[col]);
+            } else {
+              bv = load_bias_f32(p.bias, p.bias_dtype, col);
+              if (p.epilogue == TI_EPI_SCALE_BIAS || p.epilogue == TI_EPI_SCALE_BIAS_RELU) bv = __fmul_rn(bv, beta);
+            }
+          }
+          bias_s[c] = bv;
+        }
+        mbar_arrive(bias_ready_bar);
+        if (!mbar_wait(bias_ready_bar, (uint32_t)local & 1u, abort_flag)) {
+          if (lane == 0) atomicOr(&g_status, STATUS_EPILOGUE);
+          ok = false;
+          break;
+        }
+      }
       if (!mbar_wait(acc_full_bar(buf), use & 1u, abort_flag)) {
         if (lane == 0) atomicOr(&g_status, STATUS_EPILOGUE);
         ok = false;
         break;
       }
       tc_fence_after();
-      const int row = tile.m_blk * BM + quarter * 32 + lane;
+      const int row0 = tile.m_blk * BM + quarter * 32;
+      const int row = row0 + lane;
       const bool row_ok = row < p.m;
-      const int col0 = tile.n_blk * BN;
       OutT* c_row = reinterpret_cast<OutT*>(p.c) + (int64_t)tile.batch * p.c_stride_batch + (int64_t)row * p.c_stride_m;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
-#pragma unroll 1
-      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+
+      auto emit = [&](const int chunk, const uint32_t (&r)[32]) {
         const int col = col0 + chunk * 32;
-        if (col >= p.n) break;  // uniform across the warp
-        uint32_t r[32];
-        tmem_ld32(taddr + (uint32_t)(chunk * 32), r);
-        tmem_ld_wait();
-        const int ncols = min(32, p.n - col);
         alignas(16) OutT v[32];
-        if (p.epilogue == TI_EPI_I32) {
-          if constexpr (sizeof(OutT) == 4) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              int32_t a = (int32_t)r[j];
-              if (p.bias != nullptr && j < ncols) a += ((const int32_t*)p.bias)[col + j];
-              reinterpret_cast<int32_t*>(v)[j] = a;
-            }
+        if (col < p.n) epilogue_chunk<OutT>(r, has_bias ? bias_s + chunk * 32 : nullptr, alpha, beta, p.epilogue, p.rounding, v);
+        if (p.c_tma_ok) {
+          const int sub = chunk % CHUNKS_PER_BUF;
+          const uint32_t buf_addr = stage_base + (uint32_t)(out_buf * S::OUT_BUF_BYTES);
+          if (sub == 0) {
+            // the store issued from this buffer two fills ago must have finished reading it
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
           }
-        } else {
+          const uint32_t* vw = reinterpret_cast<const uint32_t*>(v);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float b = 0.f;
-            if (p.bias != nullptr && j < ncols) b = load_bias_f32(p.bias, p.bias_dtype, col + j);
-            float f = epilogue_f32((int32_t)r[j], b, alpha, beta, p.epilogue);
-            OutT o = OutCast<OutT>::from(f, p.rounding);
-            if constexpr (sizeof(OutT) == 1) {
-              if (p.epilogue == TI_EPI_SCALE_BIAS_RELU) o = o < 0 ? (OutT)0 : o;
-            }
-            v[j] = o;
+          for (int i = 0; i < NV; ++i) {
+            const int lc = sub * NV + i;
+            const int pc = SWZ ? (lc ^ (lane & 7)) : lc;
+            st_shared_v4(buf_addr + (uint32_t)(lane * ROW_BYTES + pc * 16), vw[4 * i], vw[4 * i + 1], vw[4 * i + 2], vw[4 * i + 3]);
           }
+          if (sub == CHUNKS_PER_BUF - 1) {
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              const int bcol = col0 + (chunk / CHUNKS_PER_BUF) * COLS_PER_BUF;
+              if (bcol < p.n && row0 < p.m) tma_store_3d(&map_c, buf_addr, bcol, row0, tile.batch);
+              tma_store_commit();
+            }
+            out_buf ^= 1;
+          }
+        } else if (row_ok && col < p.n) {
+          store_row32<OutT>(c_row + (int64_t)col * p.c_stride_n, v, min(32, p.n - col), p.c_vec_ok != 0, p.c_stride_n);
         }
-        if (row_ok) store_row32<OutT>(c_row + (int64_t)col * p.c_stride_n, v, ncols, p.c_vec_ok != 0, p.c_stride_n);
+      };
+
+      uint32_t r0[32], r1[32];
+      tmem_ld32(taddr, r0);
+#pragma unroll 1
+      for (int c = 0; c < NCHUNK; c += 2) {
+        tmem_ld_wait();
+        tmem_ld32(taddr + (uint32_t)((c + 1) * 32), r1);
+        emit(c, r0);
+        tmem_ld_wait();
+        if (c + 2 < NCHUNK) {
+          tmem_ld32(taddr + (uint32_t)((c + 2) * 32), r0);
+        } else {
+          // every accumulator of this buffer is in registers: hand it back to the MMA warp
+          tc_fence_before();
+          mbar_arrive(acc_empty_bar(buf));
+        }
+        emit(c + 1, r1);
       }
-      tc_fence_before();
-      mbar_arrive(acc_empty_bar(buf));
+      if (has_bias) mbar_arrive(bias_free_bar);
       ++local;
     }
+    if (lane == 0) tma_store_wait_all();
+    __syncwarp();
   }
 
   // ---------------------------------------------------------------- teardown
@@ -438,6 +584,25 @@ inline int make_operand_map(CUtensorMap* map, const void* base, int64_t k, int64
   return TI_OK;
 }
 
+// Tensor map over the output viewed as [batch][m][n], n contiguous; box = 32 rows x one
+// staged row (128 bytes, 128B-swizzled, or a narrower unswizzled row for small tiles).
+inline int make_output_map(CUtensorMap* map, void* base, int esz, int64_t n, int64_t m, int64_t batch,
+                           int64_t row_stride, int64_t batch_stride, int box_cols, bool swizzle128) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return TI_ERR_CUDA;
+  const CUtensorMapDataType dt = esz == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                               : esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
+  cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)(row_stride * esz), (cuuint64_t)((batch > 1 ? batch_stride : row_stride * m) * esz)};
+  if (strides[1] == 0 || (strides[1] % 16) != 0) strides[1] = 16;
+  cuuint32_t box[3] = {(cuuint32_t)box_cols, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, dt, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? TI_OK : TI_ERR_CUDA;
+}
+
 // True when the tensor-map path can address this problem: both operands K-contiguous,
 // 16-byte aligned bases and 16-byte multiple row/batch strides.
 inline bool eligible(const ti_gemm_params& g) {
@@ -490,8 +655,17 @@ int launch_cfg(const ti_gemm_params& g, int num_sms) {
     TI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::DYN_BYTES));
     attr_set = true;
   }
+  CUtensorMap map_c;
+  memset(&map_c, 0, sizeof(map_c));
+  p.c_tma_ok = 0;
+  if (p.c_vec_ok) {
+    constexpr int ROW_BYTES = (BN * (int)sizeof(OutT) < 128) ? BN * (int)sizeof(OutT) : 128;
+    if (make_output_map(&map_c, g.c, (int)sizeof(OutT), g.n, g.m, g.batch, g.c_stride_m, g.c_stride_batch,
+                        ROW_BYTES / (int)sizeof(OutT), ROW_BYTES == 128) == TI_OK)
+      p.c_tma_ok = 1;
+  }
   const int grid = p.num_tiles < num_sms ? p.num_tiles : num_sms;
-  kern<<<grid, NUM_THREADS, S::DYN_BYTES, (cudaStream_t)g.stream>>>(map_a, map_b, p);
+  kern<<<grid, NUM_THREADS, S::DYN_BYTES, (cudaStream_t)g.stream>>>(map_a, map_b, map_c, p);
   count_launch();
   TI_CUDA_CHECK(cudaGetLastError());
   return TI_OK;

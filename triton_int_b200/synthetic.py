@@ -102,6 +102,14 @@ def config4_block(seed: int = 3, hidden: int = 4096, heads: int = 32, ffn: int =
     p["fc1_bias"] = torch.randn((ffn,), generator=g) * 0.1
     p["fc2_w"] = int8_normal((hidden, ffn), 30.0, g)
     p["fc2_bias"] = int32_normal((hidden,), 1.0e3, g)
+    # dequantisation scales of the int32-emitting linears and fc1's alpha: drawn from the
+    # same U(1e-3,1e-2) and divided by a power of two so dequantised values stay O(1)
+    p["prev_scale"] = scale() / 64.0
+    p["out_scale"] = scale() / 256.0
+    p["fc1_alpha"] = scale() / 128.0
+    p["fc1_mul"] = torch.tensor(1.0 / 0.02, dtype=torch.float32)
+    p["qk_alpha"] = torch.tensor(1e-3, dtype=torch.float32)
+    p["pv_alpha"] = torch.tensor(8e-3, dtype=torch.float32)
     p["residual"] = torch.randn((t, hidden), generator=g)
     p["prev_acc"] = int32_normal((t, hidden), 2.0e4, g)
     p["meta"] = dict(hidden=hidden, heads=heads, ffn=ffn, batch=batch, seq=seq, eps=1e-5)
