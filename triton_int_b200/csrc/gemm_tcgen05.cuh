@@ -6,8 +6,9 @@
 //   warp 1      allocates TMEM, then one lane issues tcgen05.mma kind::i8
 //               (M=128, N=BN, K=32 per instruction, 4 per stage) into one of two
 //               TMEM accumulator buffers and commits stage/accumulator barriers
-//   warps 2..5  epilogue: tcgen05.ld the int32 accumulator (each warp owns the 32
-//               TMEM lanes of its quarter), apply the fused fp32 epilogue, stage
+//   warps 2..9  epilogue: tcgen05.ld the int32 accumulator (warp w owns the 32 TMEM
+//               lanes of quarter w%4 and one half of the tile's columns; two warps
+//               per scheduler hide each other's latencies), apply the fused fp32 epilogue, stage
 //               128-byte output rows in swizzled shared memory and write them
 //               with TMA tensor stores (which clip ragged edges); outputs TMA
 //               cannot address fall back to per-row vector/scalar stores
@@ -17,6 +18,7 @@
 
 #include <cuda.h>
 #include <cstring>
+#include <type_traits>
 
 #include "ti_common.cuh"
 
@@ -26,8 +28,8 @@ namespace tc {
 constexpr int BM = 128;          // rows of A per tile = TMEM lanes
 constexpr int BK = 128;          // bytes of K per stage = one 128B swizzle row
 constexpr int UMMA_K = 32;       // K per tcgen05.mma kind::i8
-constexpr int NUM_THREADS = 192; // 6 warps
-constexpr int NUM_EPI_THREADS = 128;
+constexpr int NUM_THREADS = 320; // 10 warps
+constexpr int NUM_EPI_THREADS = 256;
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
 struct Params {
@@ -110,7 +112,6 @@ __device__ __forceinline__ void tma_store_wait_read() {
 }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -208,10 +209,10 @@ struct Smem {
   static constexpr int B_BYTES = BN * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
-  // output staging: 4 epilogue warps x 2 buffers x (32 rows x 128 bytes)
+  // output staging: 8 epilogue warps x (32 rows x 128 bytes)
   static constexpr int OUT_BUF_BYTES = 32 * 128;
   static constexpr int OUT_OFFSET = TILE_BYTES;
-  static constexpr int OUT_BYTES = 4 * 2 * OUT_BUF_BYTES;
+  static constexpr int OUT_BYTES = 8 * OUT_BUF_BYTES;
   // per-tile bias row (fp32 or raw int32 bits)
   static constexpr int BIAS_OFFSET = OUT_OFFSET + OUT_BYTES;
   static constexpr int BIAS_BYTES = BN * 4;
@@ -240,57 +241,106 @@ __device__ __forceinline__ void store_row32(OutT* dst, const OutT (&v)[32], int 
   }
 }
 
-// 32 accumulators of one row -> 32 outputs.  `bias_c` points at this chunk's 32
+// float -> int8 (round half to even, saturate) without the conversion unit: clamp,
+// then add 1.5 * 2^23 so the fp32 adder rounds to an integer that sits in the low
+// mantissa bits; the low byte of the result is the two's-complement int8.
+__device__ __forceinline__ uint32_t quant_rne_sat_bits(float f) {
+  f = fminf(fmaxf(f, -128.0f), 127.0f);
+  return __float_as_uint(__fadd_rn(f, 12582912.0f));
+}
+__device__ __forceinline__ uint32_t pack4_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
+// GELU-quant value before the int8 cast: gelu_tanh(x) * scale with
+// 0.5*x*(1+tanh(u)) rewritten as x - x / (exp(2u) + 1) (two special-function
+// operations per element).  Differs from the operation-by-operation form of
+// ti::gelu_tanh_scaled by a few fp32 ulps.
+__device__ __forceinline__ float gelu_q_fast(float x, float scale) {
+  const float c2 = 2.302208198f;       // 2 * sqrt(2/pi) * log2(e)
+  const float c2k = 0.1029432397f;     // c2 * 0.044715
+  const float u = __fmul_rn(x, __fmaf_rn(__fmul_rn(x, x), c2k, c2));
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(u));
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(__fadd_rn(e, 1.0f)));
+  return __fmul_rn(__fmaf_rn(-x, r, x), scale);
+}
+
+// 32 accumulators of one row -> 32 outputs packed into 32-bit words (8 words of
+// int8, 16 of fp16/bf16, 32 of fp32/int32).  `bias_c` points at this chunk's 32
 // staged bias values in shared memory (already multiplied by beta for the
 // scale+bias epilogues; raw int32 bits for the int32 epilogue) or is null.
-template <typename OutT>
+template <typename OutT, int epilogue>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const float* bias_c, float alpha, float beta,
-                                               int epilogue, int rounding, OutT (&v)[32]) {
-  switch (epilogue) {
-    case TI_EPI_I32:
-      if constexpr (sizeof(OutT) == 4) {
+                                               int rounding, uint32_t (&vw)[8 * sizeof(OutT)]) {
+  float f[32];
+  if constexpr (epilogue == TI_EPI_I32) {
+    if constexpr (std::is_same<OutT, int32_t>::value) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          int32_t a = (int32_t)r[j];
-          if (bias_c) a += __float_as_int(bias_c[j]);
-          reinterpret_cast<int32_t*>(v)[j] = a;
+      for (int j = 0; j < 32; ++j) vw[j] = r[j] + (bias_c ? __float_as_uint(bias_c[j]) : 0u);
+    }
+    return;
+  }
+  if constexpr (epilogue == TI_EPI_SCALE) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __fmul_rn(__int2float_rn((int32_t)r[j]), alpha);
+  } else if constexpr (epilogue == TI_EPI_GELU_Q) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float x = __fadd_rn(__fmul_rn(__int2float_rn((int32_t)r[j]), alpha), bias_c ? bias_c[j] : 0.f);
+      f[j] = gelu_q_fast(x, beta);
+    }
+  } else {  // scale + bias (+ ReLU)
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      f[j] = __fadd_rn(bias_c ? bias_c[j] : 0.f, __fmul_rn(__int2float_rn((int32_t)r[j]), alpha));
+  }
+  if constexpr (std::is_same<OutT, int8_t>::value) {
+    constexpr bool relu = (epilogue == TI_EPI_SCALE_BIAS_RELU);
+    if (rounding == TI_ROUND_RNE_SAT) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        uint32_t b[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) b[i] = quant_rne_sat_bits(relu ? fmaxf(f[j + i], 0.f) : f[j + i]);
+        vw[j >> 2] = pack4_low_bytes(b[0], b[1], b[2], b[3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        uint32_t b[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          int8_t o = cast_i8(f[j + i], TI_ROUND_TRUNC_WRAP);
+          if (relu && o < 0) o = 0;  // ReLU after the wrapping cast, as the reference orders it
+          b[i] = (uint32_t)(uint8_t)o;
         }
+        vw[j >> 2] = pack4_low_bytes(b[0], b[1], b[2], b[3]);
       }
-      break;
-    case TI_EPI_SCALE:
+    }
+  } else if constexpr (std::is_same<OutT, int32_t>::value) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        v[j] = OutCast<OutT>::from(__fmul_rn(__int2float_rn((int32_t)r[j]), alpha), rounding);
-      break;
-    case TI_EPI_SCALE_BIAS:
+    for (int j = 0; j < 32; ++j) vw[j] = (uint32_t)__float2int_rz(f[j]);
+  } else if constexpr (std::is_same<OutT, float>::value) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float b = bias_c ? bias_c[j] : 0.f;
-        v[j] = OutCast<OutT>::from(__fadd_rn(b, __fmul_rn(__int2float_rn((int32_t)r[j]), alpha)), rounding);
-      }
-      break;
-    case TI_EPI_SCALE_BIAS_RELU:
-      if constexpr (sizeof(OutT) == 1) {
+    for (int j = 0; j < 32; ++j) vw[j] = __float_as_uint(f[j]);
+  } else if constexpr (std::is_same<OutT, __half>::value) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float b = bias_c ? bias_c[j] : 0.f;
-          const OutT o = OutCast<OutT>::from(__fadd_rn(b, __fmul_rn(__int2float_rn((int32_t)r[j]), alpha)), rounding);
-          v[j] = o < 0 ? (OutT)0 : o;  // ReLU after the int8 cast, as the reference orders it
-        }
-      }
-      break;
-    case TI_EPI_GELU_Q:
+    for (int j = 0; j < 32; j += 2) {
+      const __half2 h = __floats2half2_rn(f[j], f[j + 1]);
+      vw[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float b = bias_c ? bias_c[j] : 0.f;
-        const float x = __fadd_rn(__fmul_rn(__int2float_rn((int32_t)r[j]), alpha), b);
-        v[j] = OutCast<OutT>::from(gelu_tanh_scaled(x, beta), rounding);
-      }
-      break;
+    for (int j = 0; j < 32; j += 2) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(f[j], f[j + 1]);
+      vw[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+    }
   }
 }
 
-template <int BN, int STAGES, typename OutT>
+template <int BN, int STAGES, typename OutT, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                        const __grid_constant__ CUtensorMap map_c, const Params p) {
@@ -407,22 +457,23 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     }
   } else {
     // ------------------------------------------------------------ epilogue warps
-    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+    const int quarter = warp & 3;       // TMEM lanes [32*quarter, 32*quarter+32)
+    const int half = (warp - 2) >> 2;   // which half of the tile's columns
     const int epi_tid = threadIdx.x - 64;
     const float alpha = p.alpha ? *p.alpha : 1.0f;
     const float beta = p.beta ? *p.beta : 1.0f;
     constexpr int ESZ = (int)sizeof(OutT);
-    constexpr int ROW_BYTES = (BN * ESZ < 128) ? BN * ESZ : 128;  // one staged output row
+    constexpr int HALF_N = BN / 2;
+    constexpr int ROW_BYTES = (HALF_N * ESZ < 128) ? HALF_N * ESZ : 128;  // one staged output row
     constexpr int COLS_PER_BUF = ROW_BYTES / ESZ;
     constexpr int CHUNKS_PER_BUF = COLS_PER_BUF / 32;
     constexpr bool SWZ = (ROW_BYTES == 128);
     constexpr int NV = 32 * ESZ / 16;  // 16-byte pieces per 32-column chunk
-    constexpr int NCHUNK = BN / 32;
-    static_assert(CHUNKS_PER_BUF >= 1 && NCHUNK % 2 == 0, "tile width");
+    constexpr int NCH = HALF_N / 32;   // 32-column chunks per warp
+    static_assert(CHUNKS_PER_BUF >= 1 && NCH >= 1, "tile width");
     float* bias_s = reinterpret_cast<float*>(smem + S::BIAS_OFFSET);
-    const uint32_t stage_base = smem_base + S::OUT_OFFSET + (uint32_t)((warp - 2) * 2 * S::OUT_BUF_BYTES);
+    const uint32_t buf_addr = smem_base + S::OUT_OFFSET + (uint32_t)((warp - 2) * S::OUT_BUF_BYTES);
     const bool has_bias = p.bias != nullptr;
-    int out_buf = 0;
     int local = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
@@ -442,11 +493,11 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           const int col = col0 + c;
           float bv = 0.f;
           if (col < p.n) {
-            if (p.epilogue == TI_EPI_I32) {
+            if constexpr (EPI == TI_EPI_I32) {
               bv = __int_as_float(((const int32_t*)p.bias)[col]);
             } else {
               bv = load_bias_f32(p.bias, p.bias_dtype, col);
-              if (p.epilogue == TI_EPI_SCALE_BIAS || p.epilogue == TI_EPI_SCALE_BIAS_RELU) bv = __fmul_rn(bv, beta);
+              if constexpr (EPI == TI_EPI_SCALE_BIAS || EPI == TI_EPI_SCALE_BIAS_RELU) bv = __fmul_rn(bv, beta);
             }
           }
           bias_s[c] = bv;
@@ -468,21 +519,21 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       const int row = row0 + lane;
       const bool row_ok = row < p.m;
       OutT* c_row = reinterpret_cast<OutT*>(p.c) + (int64_t)tile.batch * p.c_stride_batch + (int64_t)row * p.c_stride_m;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * HALF_N);
 
       auto emit = [&](const int chunk, const uint32_t (&r)[32]) {
-        const int col = col0 + chunk * 32;
-        alignas(16) OutT v[32];
-        if (col < p.n) epilogue_chunk<OutT>(r, has_bias ? bias_s + chunk * 32 : nullptr, alpha, beta, p.epilogue, p.rounding, v);
+        const int ccol = half * HALF_N + chunk * 32;  // column inside the tile
+        const int col = col0 + ccol;
+        alignas(16) uint32_t vw[8 * ESZ];
+        if (col < p.n)
+          epilogue_chunk<OutT, EPI>(r, has_bias ? bias_s + ccol : nullptr, alpha, beta, p.rounding, vw);
         if (p.c_tma_ok) {
           const int sub = chunk % CHUNKS_PER_BUF;
-          const uint32_t buf_addr = stage_base + (uint32_t)(out_buf * S::OUT_BUF_BYTES);
           if (sub == 0) {
-            // the store issued from this buffer two fills ago must have finished reading it
-            if (lane == 0) tma_store_wait_read<1>();
+            // the previous store issued from this warp's buffer must have finished reading it
+            if (lane == 0) tma_store_wait_read<0>();
             __syncwarp();
           }
-          const uint32_t* vw = reinterpret_cast<const uint32_t*>(v);
 #pragma unroll
           for (int i = 0; i < NV; ++i) {
             const int lc = sub * NV + i;
@@ -493,33 +544,31 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             fence_async_smem();
             __syncwarp();
             if (lane == 0) {
-              const int bcol = col0 + (chunk / CHUNKS_PER_BUF) * COLS_PER_BUF;
+              const int bcol = col0 + half * HALF_N + (chunk / CHUNKS_PER_BUF) * COLS_PER_BUF;
               if (bcol < p.n && row0 < p.m) tma_store_3d(&map_c, buf_addr, bcol, row0, tile.batch);
               tma_store_commit();
             }
-            out_buf ^= 1;
           }
         } else if (row_ok && col < p.n) {
-          store_row32<OutT>(c_row + (int64_t)col * p.c_stride_n, v, min(32, p.n - col), p.c_vec_ok != 0, p.c_stride_n);
+          store_row32<OutT>(c_row + (int64_t)col * p.c_stride_n, *reinterpret_cast<const OutT(*)[32]>(vw),
+                            min(32, p.n - col), p.c_vec_ok != 0, p.c_stride_n);
         }
       };
+      auto release_acc = [&]() {
+        // every accumulator this warp needs is in registers: hand the buffer back to the MMA warp
+        tc_fence_before();
+        mbar_arrive(acc_empty_bar(buf));
+      };
 
-      uint32_t r0[32], r1[32];
-      tmem_ld32(taddr, r0);
+      // one call site for the chunk body keeps the instruction footprint small; the two
+      // epilogue warps of each scheduler cover each other's TMEM-load latency
 #pragma unroll 1
-      for (int c = 0; c < NCHUNK; c += 2) {
+      for (int c = 0; c < NCH; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + (uint32_t)(c * 32), r);
         tmem_ld_wait();
-        tmem_ld32(taddr + (uint32_t)((c + 1) * 32), r1);
-        emit(c, r0);
-        tmem_ld_wait();
-        if (c + 2 < NCHUNK) {
-          tmem_ld32(taddr + (uint32_t)((c + 2) * 32), r0);
-        } else {
-          // every accumulator of this buffer is in registers: hand it back to the MMA warp
-          tc_fence_before();
-          mbar_arrive(acc_empty_bar(buf));
-        }
-        emit(c + 1, r1);
+        if (c == NCH - 1) release_acc();
+        emit(c, r);
       }
       if (has_bias) mbar_arrive(bias_free_bar);
       ++local;
@@ -617,7 +666,7 @@ inline bool eligible(const ti_gemm_params& g) {
   return true;
 }
 
-template <int BN, int STAGES, typename OutT>
+template <int BN, int STAGES, typename OutT, int EPI>
 int launch_cfg(const ti_gemm_params& g, int num_sms) {
   using S = Smem<BN, STAGES>;
   CUtensorMap map_a, map_b;
@@ -649,7 +698,7 @@ int launch_cfg(const ti_gemm_params& g, int num_sms) {
   p.c_vec_ok = (g.c_stride_n == 1) && (((uintptr_t)g.c & 15) == 0) && ((g.c_stride_m * esz) % 16 == 0) &&
                ((g.c_stride_batch * esz) % 16 == 0);
 
-  auto kern = gemm_i8_tcgen05_kernel<BN, STAGES, OutT>;
+  auto kern = gemm_i8_tcgen05_kernel<BN, STAGES, OutT, EPI>;
   static bool attr_set = false;
   if (!attr_set) {
     TI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::DYN_BYTES));
@@ -659,7 +708,7 @@ int launch_cfg(const ti_gemm_params& g, int num_sms) {
   memset(&map_c, 0, sizeof(map_c));
   p.c_tma_ok = 0;
   if (p.c_vec_ok) {
-    constexpr int ROW_BYTES = (BN * (int)sizeof(OutT) < 128) ? BN * (int)sizeof(OutT) : 128;
+    constexpr int ROW_BYTES = ((BN / 2) * (int)sizeof(OutT) < 128) ? (BN / 2) * (int)sizeof(OutT) : 128;
     if (make_output_map(&map_c, g.c, (int)sizeof(OutT), g.n, g.m, g.batch, g.c_stride_m, g.c_stride_batch,
                         ROW_BYTES / (int)sizeof(OutT), ROW_BYTES == 128) == TI_OK)
       p.c_tma_ok = 1;
@@ -671,23 +720,42 @@ int launch_cfg(const ti_gemm_params& g, int num_sms) {
   return TI_OK;
 }
 
-template <typename OutT>
-int launch_out(const ti_gemm_params& g, int num_sms) {
+template <typename OutT, int EPI>
+int launch_epi(const ti_gemm_params& g, int num_sms) {
   // 128x256 tiles when N is wide enough to fill them, else 128x128 / 128x64
-  if (g.n > 128) return launch_cfg<256, 4, OutT>(g, num_sms);
-  if (g.n > 64) return launch_cfg<128, 6, OutT>(g, num_sms);
-  return launch_cfg<64, 8, OutT>(g, num_sms);
+  if (g.n > 128) return launch_cfg<256, 4, OutT, EPI>(g, num_sms);
+  if (g.n > 64) return launch_cfg<128, 6, OutT, EPI>(g, num_sms);
+  return launch_cfg<64, 8, OutT, EPI>(g, num_sms);
 }
 
 inline int launch(const ti_gemm_params& g, int num_sms) {
+  const int ep = g.epilogue;
   switch (g.out_dtype) {
-    case TI_I8: return launch_out<int8_t>(g, num_sms);
-    case TI_I32: return launch_out<int32_t>(g, num_sms);
-    case TI_F32: return launch_out<float>(g, num_sms);
-    case TI_F16: return launch_out<__half>(g, num_sms);
-    case TI_BF16: return launch_out<__nv_bfloat16>(g, num_sms);
+    case TI_I8:
+      if (ep == TI_EPI_SCALE) return launch_epi<int8_t, TI_EPI_SCALE>(g, num_sms);
+      if (ep == TI_EPI_SCALE_BIAS) return launch_epi<int8_t, TI_EPI_SCALE_BIAS>(g, num_sms);
+      if (ep == TI_EPI_SCALE_BIAS_RELU) return launch_epi<int8_t, TI_EPI_SCALE_BIAS_RELU>(g, num_sms);
+      if (ep == TI_EPI_GELU_Q) return launch_epi<int8_t, TI_EPI_GELU_Q>(g, num_sms);
+      break;
+    case TI_I32:
+      if (ep == TI_EPI_I32) return launch_epi<int32_t, TI_EPI_I32>(g, num_sms);
+      if (ep == TI_EPI_SCALE) return launch_epi<int32_t, TI_EPI_SCALE>(g, num_sms);
+      if (ep == TI_EPI_SCALE_BIAS) return launch_epi<int32_t, TI_EPI_SCALE_BIAS>(g, num_sms);
+      break;
+    case TI_F32:
+      if (ep == TI_EPI_SCALE) return launch_epi<float, TI_EPI_SCALE>(g, num_sms);
+      if (ep == TI_EPI_SCALE_BIAS) return launch_epi<float, TI_EPI_SCALE_BIAS>(g, num_sms);
+      break;
+    case TI_F16:
+      if (ep == TI_EPI_SCALE) return launch_epi<__half, TI_EPI_SCALE>(g, num_sms);
+      if (ep == TI_EPI_SCALE_BIAS) return launch_epi<__half, TI_EPI_SCALE_BIAS>(g, num_sms);
+      break;
+    case TI_BF16:
+      if (ep == TI_EPI_SCALE) return launch_epi<__nv_bfloat16, TI_EPI_SCALE>(g, num_sms);
+      if (ep == TI_EPI_SCALE_BIAS) return launch_epi<__nv_bfloat16, TI_EPI_SCALE_BIAS>(g, num_sms);
+      break;
   }
-  set_error("unsupported output dtype %d", g.out_dtype);
+  set_error("unsupported output dtype / epilogue combination (%d, %d)", g.out_dtype, ep);
   return TI_ERR_DTYPE;
 }
 

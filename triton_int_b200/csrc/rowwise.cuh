@@ -108,7 +108,7 @@ struct LnParams {
 // XT: float / half / bf16 / int32 (dequant+residual).  PT: dtype of gamma, beta, skip and
 // of a non-int8 output.  QOUT: int8 output.  MAXV float4-groups per thread.
 template <typename XT, typename PT, bool QOUT, int MAXV>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(512, (MAXV <= 4 ? 3 : (MAXV == 8 ? 2 : 1)))
 layernorm_vec_kernel(const LnParams p, const int tpr) {
   __shared__ float red[32 * 32];
   const int rows_per_cta = blockDim.x / tpr;
@@ -267,10 +267,10 @@ layernorm_any_kernel(const LnParams p) {
   }
 }
 
-inline int pick_tpr(int64_t n, int* maxv) {
-  // about 16 elements per thread, 32..512 threads per row
+inline int pick_tpr(int64_t n, int* maxv, int per_thread = 16) {
+  // about `per_thread` elements per thread, 32..512 threads per row
   int tpr = 32;
-  while (tpr < 512 && (int64_t)tpr * 16 < n) tpr <<= 1;
+  while (tpr < 512 && (int64_t)tpr * per_thread < n) tpr <<= 1;
   int64_t v = (n + (int64_t)tpr * 4 - 1) / ((int64_t)tpr * 4);
   int mv = 1;
   while (mv < v) mv <<= 1;
@@ -377,12 +377,24 @@ gelu_q_kernel(const int8_t* __restrict__ x, int8_t* __restrict__ y, int64_t n, f
     const int64_t nvec = n >> 4;
     const uint4* xv = reinterpret_cast<const uint4*>(x);
     uint4* yv = reinterpret_cast<uint4*>(y);
-    for (int64_t i = gtid; i < nvec; i += stride) {
+    // four independent 16-byte loads in flight per thread
+    int64_t i = gtid;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = __ldcs(xv + i + u * stride);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        v[u].x = word(v[u].x); v[u].y = word(v[u].y); v[u].z = word(v[u].z); v[u].w = word(v[u].w);
+        __stcs(yv + i + u * stride, v[u]);
+      }
+    }
+    for (; i < nvec; i += stride) {
       uint4 v = __ldcs(xv + i);
       v.x = word(v.x); v.y = word(v.y); v.z = word(v.z); v.w = word(v.w);
       __stcs(yv + i, v);
     }
-    for (int64_t i = (nvec << 4) + gtid; i < n; i += stride) y[i] = (int8_t)look((uint8_t)x[i]);
+    for (int64_t j = (nvec << 4) + gtid; j < n; j += stride) y[j] = (int8_t)look((uint8_t)x[j]);
   } else {
     for (int64_t i = gtid; i < n; i += stride) y[i] = (int8_t)look((uint8_t)x[i]);
   }
@@ -413,8 +425,14 @@ struct SmParams {
   int causal, rounding;
 };
 
+__device__ __forceinline__ float exp2_approx(float x) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x));
+  return e;
+}
+
 template <int MAXV, bool VEC>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(512, (MAXV <= 4 ? 3 : (MAXV == 8 ? 2 : 1)))
 softmax_q_kernel(const SmParams p, const int tpr) {
   __shared__ float red[32 * 32];
   const int rows_per_cta = blockDim.x / tpr;
@@ -427,17 +445,19 @@ softmax_q_kernel(const SmParams p, const int tpr) {
   const int n = (int)p.n;
   // number of visible keys of this query row
   int64_t vis64 = p.causal ? (i + (p.n - p.m) + 1) : p.n;
-  const int vis = (int)(vis64 < 0 ? 0 : (vis64 > p.n ? p.n : vis64));
+  const int vis = row_ok ? (int)(vis64 < 0 ? 0 : (vis64 > p.n ? p.n : vis64)) : 0;
   const float* srow = p.s + b * p.s_batch_stride + i * p.s_row_stride;
   int8_t* prow = p.p + b * p.p_batch_stride + i * p.p_row_stride;
   const float NEG_INF = __int_as_float(0xff800000);
+  const float LOG2E = 1.4426950408889634f;
 
+  // masked positions are never loaded; they hold -inf and come out as exact zeros
   float v[MAXV][4];
 #pragma unroll
   for (int k = 0; k < MAXV; ++k) {
     const int col = (k * tpr + tid) * 4;
     v[k][0] = v[k][1] = v[k][2] = v[k][3] = NEG_INF;
-    if (row_ok && col < vis) {
+    if (col < vis) {
       if (VEC && col + 4 <= n) {
         Vec4<float>::load(srow + col, v[k]);
       } else {
@@ -452,27 +472,35 @@ softmax_q_kernel(const SmParams p, const int tpr) {
 #pragma unroll
   for (int k = 0; k < MAXV; ++k) mx = fmaxf(mx, fmaxf(fmaxf(v[k][0], v[k][1]), fmaxf(v[k][2], v[k][3])));
   mx = row_reduce<true>(mx, tpr, tid, row_in_cta, red);
+  // exp(s - max) = 2^((s - max) * log2 e); 2^-inf = 0 covers the masked positions
+  const float mxl = (vis > 0) ? mx * LOG2E : 0.f;
   float sum = 0.f;
 #pragma unroll
   for (int k = 0; k < MAXV; ++k) {
+    const int col = (k * tpr + tid) * 4;
+    if (col < vis) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float e = (v[k][j] == NEG_INF) ? 0.f : expf(v[k][j] - mx);
-      v[k][j] = e;
-      sum += e;
+      for (int j = 0; j < 4; ++j) {
+        const float e = exp2_approx(v[k][j] * LOG2E - mxl);
+        v[k][j] = e;
+        sum += e;
+      }
     }
   }
   sum = row_reduce<false>(sum, tpr, tid, row_in_cta, red);
-  const float inv = (vis > 0) ? 1.0f / sum : 0.f;
+  const float inv = (vis > 0) ? p.out_mul / sum : 0.f;
 #pragma unroll
   for (int k = 0; k < MAXV; ++k) {
     const int col = (k * tpr + tid) * 4;
     if (!(row_ok && col < n)) continue;
-    float o[4];
+    float o[4] = {0.f, 0.f, 0.f, 0.f};
+    if (col < vis) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) o[j] = (v[k][j] * inv) * p.out_mul;
+      for (int j = 0; j < 4; ++j) o[j] = v[k][j] * inv;
+    }
     if (VEC && col + 4 <= n) {
-      Vec4<int8_t>::store_q(prow + col, o, p.rounding);
+      if (col < vis) Vec4<int8_t>::store_q(prow + col, o, p.rounding);
+      else *reinterpret_cast<uint32_t*>(prow + col) = 0u;
     } else {
 #pragma unroll
       for (int j = 0; j < 4; ++j) if (col + j < n) prow[col + j] = cast_i8(o[j], p.rounding);
@@ -485,7 +513,7 @@ inline int launch_softmax_q(const SmParams& p, void* stream) {
   if (p.batch == 0 || p.m == 0) return TI_OK;
   if (!p.s || !p.p) { set_error("softmax_q: null pointer"); return TI_ERR_DEVICE; }
   int maxv = 0;
-  const int tpr = pick_tpr(p.n, &maxv);
+  const int tpr = pick_tpr(p.n, &maxv, 16);
   if (maxv > 16) { set_error("softmax_q: rows longer than 32768 are not supported"); return TI_ERR_UNSUPPORTED; }
   const bool vec = (((uintptr_t)p.s & 15) == 0) && (p.s_row_stride % 4 == 0) && (p.s_batch_stride % 4 == 0) &&
                    (((uintptr_t)p.p & 3) == 0) && (p.p_row_stride % 4 == 0) && (p.p_batch_stride % 4 == 0);
