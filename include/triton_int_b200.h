@@ -133,6 +133,36 @@ int ti_softmax_q(const float* s, int8_t* p, int64_t batch, int64_t m, int64_t n,
                  int64_t p_row_stride, int64_t p_batch_stride,
                  int32_t causal, float out_mul, int32_t rounding, void* stream);
 
+/*
+ * Fused int8 attention for one layer (head_dim 128):
+ *     S = alpha_qk * Q K^T ; P = int8(p_mul * softmax(mask(S))) ; O = int8(alpha_pv * P V)
+ * The composition of bmm_s8t_s8n_f32t (kernels/bmm.py:428-464), the caller's softmax
+ * and bmm_s8t_s8n_s8t (kernels/bmm.py:576-612) without materialising S or P, and
+ * without the [B*h,S,D] / V^T copies those operators need: q, k, v and o are addressed
+ * as [batch][seq][head][128] through their batch / row / head strides (elements).
+ * It has no single counterpart in the reference.  causal != 0 masks keys
+ * j > i + (seq_k - seq_q).  alpha_* are device pointers to one float each.
+ */
+typedef struct {
+  const int8_t* q;
+  const int8_t* k;
+  const int8_t* v;
+  int8_t* o;
+  const float* alpha_qk;
+  const float* alpha_pv;
+  int64_t batch, heads, seq_q, seq_k, head_dim;
+  int64_t q_stride_b, q_stride_s, q_stride_h;
+  int64_t k_stride_b, k_stride_s, k_stride_h;
+  int64_t v_stride_b, v_stride_s, v_stride_h;
+  int64_t o_stride_b, o_stride_s, o_stride_h;
+  float p_mul;
+  int32_t causal;
+  int32_t rounding;
+  void* stream;
+} ti_attention_params;
+
+int ti_attention_i8(const ti_attention_params* p);
+
 /* Reads and clears the device-side status word of the current device.  Non-zero
  * means a bounded wait inside a kernel expired (bit 0: TMA producer, bit 1: MMA
  * issuer, bit 2: epilogue).  Synchronises the device. */

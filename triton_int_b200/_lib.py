@@ -23,7 +23,7 @@ PATH_AUTO, PATH_TCGEN05, PATH_GENERIC = range(3)
 DTYPE_CODE = {torch.int8: TI_I8, torch.int32: TI_I32, torch.float32: TI_F32,
               torch.float16: TI_F16, torch.bfloat16: TI_BF16}
 
-EXPORTS = ["ti_gemm_i8", "ti_layernorm", "ti_gelu_q", "ti_softmax_q", "ti_device_status",
+EXPORTS = ["ti_gemm_i8", "ti_layernorm", "ti_gelu_q", "ti_softmax_q", "ti_attention_i8", "ti_device_status",
            "ti_version", "ti_last_error_string", "ti_launch_count", "ti_device_supported"]
 
 
@@ -56,6 +56,20 @@ class LayerNormParams(C.Structure):
     ]
 
 
+class AttentionParams(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p),
+        ("alpha_qk", C.c_void_p), ("alpha_pv", C.c_void_p),
+        ("batch", C.c_int64), ("heads", C.c_int64), ("seq_q", C.c_int64), ("seq_k", C.c_int64), ("head_dim", C.c_int64),
+        ("q_stride_b", C.c_int64), ("q_stride_s", C.c_int64), ("q_stride_h", C.c_int64),
+        ("k_stride_b", C.c_int64), ("k_stride_s", C.c_int64), ("k_stride_h", C.c_int64),
+        ("v_stride_b", C.c_int64), ("v_stride_s", C.c_int64), ("v_stride_h", C.c_int64),
+        ("o_stride_b", C.c_int64), ("o_stride_s", C.c_int64), ("o_stride_h", C.c_int64),
+        ("p_mul", C.c_float), ("causal", C.c_int32), ("rounding", C.c_int32),
+        ("stream", C.c_void_p),
+    ]
+
+
 _LIB = None
 
 
@@ -79,6 +93,8 @@ def load():
     lib.ti_gelu_q.restype = C.c_int
     lib.ti_softmax_q.argtypes = [C.c_void_p, C.c_void_p] + [C.c_int64] * 7 + [C.c_int32, C.c_float, C.c_int32, C.c_void_p]
     lib.ti_softmax_q.restype = C.c_int
+    lib.ti_attention_i8.argtypes = [C.POINTER(AttentionParams)]
+    lib.ti_attention_i8.restype = C.c_int
     lib.ti_device_status.argtypes = [C.POINTER(C.c_uint32)]
     lib.ti_device_status.restype = C.c_int
     lib.ti_version.restype = C.c_int

@@ -51,6 +51,7 @@ static int device_info(DeviceInfo* out) {
 #include "gemm_generic.cuh"
 #include "gemm_tcgen05.cuh"
 #include "rowwise.cuh"
+#include "attention_tcgen05.cuh"
 
 using namespace ti;
 
@@ -177,6 +178,21 @@ int ti_softmax_q(const float* s, int8_t* p, int64_t batch, int64_t m, int64_t n,
   sp.p_row_stride = p_row_stride; sp.p_batch_stride = p_batch_stride;
   sp.out_mul = out_mul; sp.causal = causal; sp.rounding = rounding;
   return ti::row::launch_softmax_q(sp, stream);
+}
+
+int ti_attention_i8(const ti_attention_params* a) {
+  if (!a) { set_error("attention: null params"); return TI_ERR_DEVICE; }
+  if (a->batch < 0 || a->heads < 0 || a->seq_q < 0 || a->seq_k < 0) { set_error("attention: negative extent"); return TI_ERR_SHAPE; }
+  if (a->rounding != TI_ROUND_RNE_SAT && a->rounding != TI_ROUND_TRUNC_WRAP) { set_error("attention: bad rounding mode"); return TI_ERR_UNSUPPORTED; }
+  DeviceInfo di;
+  int rc = require_device(&di);
+  if (rc != TI_OK) return rc;
+  if (a->batch * a->heads * a->seq_q > 0 &&
+      (!is_device_ptr(a->q) || !is_device_ptr(a->k) || !is_device_ptr(a->v) || !is_device_ptr(a->o))) {
+    set_error("attention: q, k, v and o must be device pointers (there is no CPU path)");
+    return TI_ERR_DEVICE;
+  }
+  return ti::attn::launch(*a, di.sms);
 }
 
 }  // extern "C"

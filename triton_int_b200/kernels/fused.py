@@ -173,3 +173,42 @@ def causal_softmax_q(s, out_mul=127.0, causal=True, out=None):
                                       config.rounding_mode(), _lib.current_stream_ptr(s.device))
     _lib.check(rc, "ti_softmax_q")
     return p
+
+
+def attention_i8(q, k, v, alpha_qk, alpha_pv, p_mul=127.0, causal=True, out=None):
+    """Fused int8 attention: int8(alpha_pv * P @ V) with P = int8(p_mul * softmax(mask(alpha_qk * Q @ K^T))).
+
+    q [B, Sq, h, 128], k and v [B, Sk, h, 128] int8 views with arbitrary batch / row /
+    head strides (for example slices of one [T, 3*H] projection buffer viewed as
+    [B, S, h, D]); returns o [B, Sq, h, 128] int8.  Equivalent to
+    bmm_s8t_s8n_f32t -> causal_softmax_q -> bmm_s8t_s8n_s8t on [B*h, S, D] operands
+    (int8 P may differ by one step at rounding boundaries because the row sum is
+    accumulated in a different order)."""
+    _lib.require_cuda(q, k, v, out)
+    assert q.dim() == 4 and k.dim() == 4 and v.dim() == 4
+    assert q.dtype == torch.int8 and k.dtype == torch.int8 and v.dtype == torch.int8
+    B, Sq, H, D = q.shape
+    assert k.shape == v.shape and k.shape[0] == B and k.shape[2] == H and k.shape[3] == D
+    Sk = k.shape[1]
+    for t in (q, k, v):
+        assert t.stride(3) == 1, "the head dimension must be contiguous"
+    o = torch.empty((B, Sq, H, D), device=q.device, dtype=torch.int8) if out is None else out
+    assert o.shape == (B, Sq, H, D) and o.dtype == torch.int8 and o.stride(3) == 1
+    dev = q.device
+    a1, a2 = scale_tensor(alpha_qk, dev), scale_tensor(alpha_pv, dev)
+    p = _lib.AttentionParams()
+    p.q, p.k, p.v, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+    p.alpha_qk, p.alpha_pv = a1.data_ptr(), a2.data_ptr()
+    p.batch, p.heads, p.seq_q, p.seq_k, p.head_dim = B, H, Sq, Sk, D
+    p.q_stride_b, p.q_stride_s, p.q_stride_h = q.stride(0), q.stride(1), q.stride(2)
+    p.k_stride_b, p.k_stride_s, p.k_stride_h = k.stride(0), k.stride(1), k.stride(2)
+    p.v_stride_b, p.v_stride_s, p.v_stride_h = v.stride(0), v.stride(1), v.stride(2)
+    p.o_stride_b, p.o_stride_s, p.o_stride_h = o.stride(0), o.stride(1), o.stride(2)
+    p.p_mul = float(p_mul)
+    p.causal = 1 if causal else 0
+    p.rounding = config.rounding_mode()
+    with torch.cuda.device(dev):
+        p.stream = _lib.current_stream_ptr(dev)
+        rc = _lib.load().ti_attention_i8(C.byref(p))
+    _lib.check(rc, "ti_attention_i8")
+    return o

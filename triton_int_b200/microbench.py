@@ -119,6 +119,15 @@ def bench_attention(bh, seq, d, iters):
     emit("causal_softmax_q", [bh, seq, seq], ms, nbytes=s.numel() * 5)
     ms = timeit(lambda: KB.bmm_s8t_s8n_s8t(p, vt, a2, out=o), iters)
     emit("bmm_s8t_s8n_s8t", [bh, seq, d, seq], ms, ops=ops, nbytes=p.numel() + 2 * o.numel())
+    # the fused kernel on the same problem laid out [B, S, h, D] (heads = 32 when bh allows)
+    heads = 32 if bh % 32 == 0 else 1
+    b = bh // heads
+    q4, k4, v4 = (t.view(b, heads, seq, d).permute(0, 2, 1, 3).contiguous() for t in (q, k, v))
+    o4 = torch.empty_like(q4)
+    ms = timeit(lambda: KF.attention_i8(q4, k4, v4, a1, a2, 127.0, causal=True, out=o4), iters)
+    # causal: about half of the score tiles; scores are computed twice, P V once
+    emit("attention_i8_fused_causal", [b, seq, heads, d], ms, ops=int(ops * 1.5 * (seq / 128 + 1) / (2 * seq / 128)),
+         nbytes=4 * q.numel())
 
 
 def main():

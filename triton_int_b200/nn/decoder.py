@@ -12,6 +12,7 @@ Data flow for T = batch * seq tokens, hidden H, P tensor-parallel ranks:
       -> DQ_Add_LayerNorm_Q          -> residual1 fp32 [T,H], x int8 [T,H]
       -> q/k/v W8A8B8O8Linear        -> int8 [T,H/P] each       (column parallel)
       -> BMM_S8T_S8N_F32T, causal softmax -> int8, BMM_S8T_S8N_S8T over H/P/D heads
+         (one fused attention kernel when head_dim is 128; the three-operator form otherwise)
       -> out_proj, raw int32 [T,H]   -> sum over ranks (exact)  (row parallel)
       -> DQ_Add_LayerNorm_Q          -> residual2 fp32 [T,H], h int8 [T,H]
       -> fc1 W8A8BFP32OFP32_GeLu_Q   -> int8 [T,F/P]            (column parallel)
@@ -27,7 +28,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels.bmm import bmm_s8t_s8n_f32t, bmm_s8t_s8n_s8t
-from ..kernels.fused import causal_softmax_q, dq_add_layernorm_q, linear_a8_w8_bfp32_ofp32_GeLu_Q
+from ..kernels.fused import attention_i8, causal_softmax_q, dq_add_layernorm_q, linear_a8_w8_bfp32_ofp32_GeLu_Q
 from ..kernels.linear import linear_a8_w8_b8_o8, linear_a8_w8_b32_o32
 
 
@@ -51,7 +52,8 @@ class Int8DecoderBlock(torch.nn.Module):
     ``reduce_fn(int32_tensor) -> int32_tensor`` performs the sum over ranks (identity
     when world == 1)."""
 
-    def __init__(self, params, rank: int = 0, world: int = 1, reduce_fn=None, causal_skip: bool = True):
+    def __init__(self, params, rank: int = 0, world: int = 1, reduce_fn=None, causal_skip: bool = True,
+                 fused_attention: bool = True):
         super().__init__()
         meta = params["meta"]
         self.hidden, self.heads, self.ffn = meta["hidden"], meta["heads"], meta["ffn"]
@@ -62,6 +64,9 @@ class Int8DecoderBlock(torch.nn.Module):
         self.head_dim = self.hidden // self.heads
         self.reduce_fn = reduce_fn if reduce_fn is not None else (lambda t: t)
         self.causal_skip = causal_skip
+        # fused attention keeps S and P on chip; the unfused form (three operators of the
+        # reference interface) is kept for comparison
+        self.fused_attention = fused_attention and self.head_dim == 128
         reg = self.register_buffer
         reg("ln1_w", params["ln1_w"].clone()); reg("ln1_b", params["ln1_b"].clone())
         reg("ln2_w", params["ln2_w"].clone()); reg("ln2_b", params["ln2_b"].clone())
@@ -90,6 +95,10 @@ class Int8DecoderBlock(torch.nn.Module):
         q = linear_a8_w8_b8_o8(x8, self.q_w, self.q_bias, self.q_alpha, self.q_beta)
         k = linear_a8_w8_b8_o8(x8, self.k_w, self.k_bias, self.k_alpha, self.k_beta)
         v = linear_a8_w8_b8_o8(x8, self.v_w, self.v_bias, self.v_alpha, self.v_beta)
+        if self.fused_attention:
+            shape = (batch, seq, self.local_heads, self.head_dim)
+            o = attention_i8(q.view(shape), k.view(shape), v.view(shape), self.qk_alpha, self.pv_alpha, 127.0, causal=True)
+            return o.view(batch * seq, self.local_heads * self.head_dim)
         qh, kh = self._heads_first(q, batch, seq), self._heads_first(k, batch, seq)
         # V^T: [B*h, D, S], the "s8n" operand of the second BMM
         vt = v.view(batch, seq, self.local_heads, self.head_dim).permute(0, 2, 3, 1).reshape(
