@@ -129,12 +129,12 @@ layernorm_vec_kernel(const LnParams p, const int tpr) {
     const int col = (i * tpr + tid) * 4;
     if (row_ok && col < n) {
       if constexpr (std::is_same<XT, int32_t>::value) {
-        int4 a = *reinterpret_cast<const int4*>((const int32_t*)p.x + row * p.x_row_stride + col);
+        int4 a = __ldcs(reinterpret_cast<const int4*>((const int32_t*)p.x + row * p.x_row_stride + col));
         if (p.bias_i32) {
           const int4 b = *reinterpret_cast<const int4*>(p.bias_i32 + col);
           a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
         }
-        const float4 r = *reinterpret_cast<const float4*>(p.residual_in + row * n + col);
+        const float4 r = __ldcs(reinterpret_cast<const float4*>(p.residual_in + row * n + col));
         // residual + scale * int32 as one fused multiply-add: what torch.add(residual,
         // int32, alpha=scale) evaluates (functional/fused.py:9)
         v[i][0] = __fmaf_rn(__int2float_rn(a.x), dq, r.x);
@@ -267,6 +267,228 @@ layernorm_any_kernel(const LnParams p) {
   }
 }
 
+// ------------------------------------------------------------------ LayerNorm, TMA-streamed rows
+// The two hot instantiations (int32 dequant + residual add -> int8, and fp32 -> int8)
+// as a persistent kernel: a producer warp streams whole rows into a shared-memory ring
+// with bulk asynchronous copies, so the bytes in flight per SM are set by the ring depth
+// and not by how many threads happen to be between their load and their store.  256
+// consumer threads pull a row into registers, free its slot, and run the same
+// arithmetic as layernorm_vec_kernel.  Several CTAs share an SM so that one CTA's
+// reductions overlap another's loads.  All mbarrier waits are bounded.
+namespace stream {
+
+constexpr int CONSUMERS = 256;
+constexpr int THREADS = CONSUMERS + 32;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (try_wait(bar, parity)) return true;
+  uint64_t t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  uint32_t spins = 0;
+  while (!try_wait(bar, parity)) {
+    if ((++spins & 255u) == 0u) {
+      if (*abort_flag) return false;
+      uint64_t t1;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+      if (t1 - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// sum over the 256 consumer threads (named barrier 1; the producer warp never joins it)
+__device__ __forceinline__ float consumer_sum(float v, float* red, int tid) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((tid & 31) == 0) red[tid >> 5] = v;
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+  return ((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]));
+}
+
+template <bool DQ, int MAXV>
+__global__ void __launch_bounds__(THREADS, 2)
+layernorm_stream_kernel(const LnParams p, const int stages) {
+  extern __shared__ __align__(128) uint8_t sm[];
+  const int n = (int)p.n;
+  const uint32_t row_bytes = (uint32_t)n * 4u;
+  const uint32_t stage_bytes = DQ ? 2u * row_bytes : row_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + (size_t)stages * stage_bytes);
+  float* red = reinterpret_cast<float*>(bars + 2 * stages);   // two banks of 8 partial sums
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(red + 16);
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + stages);
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full0 + 8 * s), "r"(1) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty0 + 8 * s), "r"(CONSUMERS) : "memory");
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (tid >= CONSUMERS) {
+    // ---- producer: one lane streams this CTA's rows into the ring
+    if (tid == CONSUMERS) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+        if (!wait(empty0 + 8 * s, ph ^ 1u, abort_flag)) { atomicOr(&g_status, STATUS_PRODUCER); break; }
+        const uint32_t dst = smem_u32(sm + (size_t)s * stage_bytes);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full0 + 8 * s), "r"(stage_bytes) : "memory");
+        bulk_load(dst, (const uint8_t*)p.x + row * p.x_row_stride * 4, row_bytes, full0 + 8 * s);
+        if (DQ) bulk_load(dst + row_bytes, p.residual_in + row * n, row_bytes, full0 + 8 * s);
+        if (++s == stages) { s = 0; ph ^= 1u; }
+      }
+    }
+    return;  // the producer warp takes no part in the consumers' named barrier
+  }
+
+  // ---- consumers
+  float dq = p.dq_scale;
+  if (DQ && p.dq_scale_dev) dq = *p.dq_scale_dev;
+  const float inv_n = 1.0f / (float)n;
+  // gamma / beta of this thread's columns stay in registers for all rows
+  float g[MAXV][4], bt[MAXV][4];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int col = (i * CONSUMERS + tid) * 4;
+    g[i][0] = g[i][1] = g[i][2] = g[i][3] = 0.f;
+    bt[i][0] = bt[i][1] = bt[i][2] = bt[i][3] = 0.f;
+    if (col < n) {
+      Vec4<float>::load((const float*)p.gamma + col, g[i]);
+      if (p.beta) Vec4<float>::load((const float*)p.beta + col, bt[i]);
+    }
+  }
+  int s = 0;
+  uint32_t ph = 0;
+  for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    const bool got = wait(full0 + 8 * s, ph, abort_flag);
+    // agree on the outcome before anyone can diverge around the named barriers below
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (!got || *abort_flag) {
+      if (tid == 0) atomicOr(&g_status, STATUS_EPILOGUE);
+      break;
+    }
+    const uint8_t* base = sm + (size_t)s * stage_bytes;
+    float v[MAXV][4];
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int col = (i * CONSUMERS + tid) * 4;
+      v[i][0] = v[i][1] = v[i][2] = v[i][3] = 0.f;
+      if (col < n) {
+        if (DQ) {
+          int4 a = *reinterpret_cast<const int4*>(base + col * 4);
+          if (p.bias_i32) {
+            const int4 b = __ldg(reinterpret_cast<const int4*>(p.bias_i32 + col));
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+          }
+          const float4 r = *reinterpret_cast<const float4*>(base + row_bytes + col * 4);
+          v[i][0] = __fmaf_rn(__int2float_rn(a.x), dq, r.x);
+          v[i][1] = __fmaf_rn(__int2float_rn(a.y), dq, r.y);
+          v[i][2] = __fmaf_rn(__int2float_rn(a.z), dq, r.z);
+          v[i][3] = __fmaf_rn(__int2float_rn(a.w), dq, r.w);
+        } else {
+          Vec4<float>::load(reinterpret_cast<const float*>(base + col * 4), v[i]);
+        }
+      }
+    }
+    // the row is in registers: hand the slot back to the producer
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8 * s) : "memory");
+    if (++s == stages) { s = 0; ph ^= 1u; }
+    if (DQ && p.residual_out) {
+#pragma unroll
+      for (int i = 0; i < MAXV; ++i) {
+        const int col = (i * CONSUMERS + tid) * 4;
+        if (col < n) __stcs(reinterpret_cast<float4*>(p.residual_out + row * n + col), make_float4(v[i][0], v[i][1], v[i][2], v[i][3]));
+      }
+    }
+    float mean = 0.f;
+    if (!p.rms) {
+      float t = 0.f;
+#pragma unroll
+      for (int i = 0; i < MAXV; ++i) t += (v[i][0] + v[i][1]) + (v[i][2] + v[i][3]);
+      mean = consumer_sum(t, red, tid) * inv_n;
+    }
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      if ((i * CONSUMERS + tid) * 4 < n) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float d = v[i][j] - mean; q += d * d; }
+      }
+    }
+    q = consumer_sum(q, red + 8, tid);
+    const float rstd = 1.0f / sqrtf(q * inv_n + p.eps);
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int col = (i * CONSUMERS + tid) * 4;
+      if (col >= n) continue;
+      float o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[j] = ((v[i][j] - mean) * rstd) * g[i][j] + bt[i][j];
+      Vec4<int8_t>::store_q((int8_t*)p.out + row * p.out_row_stride + col, o, p.rounding);
+    }
+  }
+}
+
+template <bool DQ>
+inline int launch(const LnParams& p, int num_sms, cudaStream_t st) {
+  const int64_t n = p.n;
+  int maxv = 1;
+  while ((int64_t)maxv * CONSUMERS * 4 < n) maxv <<= 1;
+  const size_t stage = (size_t)(DQ ? 8 : 4) * n;
+  // two CTAs per SM (one CTA's reductions overlap the other's loads), rings as deep as
+  // half the shared memory allows, at most 4 rows (measured best on 4096-wide rows)
+  const int per_sm = 2;
+  int stages = (int)((108 * 1024 - 256) / stage);
+  if (stages > 4) stages = 4;
+  if (stages < 2) stages = 2;
+  const size_t smem = (size_t)stages * stage + 2 * (size_t)stages * 8 + 16 * 4 + 16;
+  const int64_t want = (int64_t)num_sms * per_sm;
+  const int grid = (int)(p.rows < want ? p.rows : want);
+#define TI_LNS(MV)                                                                                         \
+  {                                                                                                        \
+    auto k = layernorm_stream_kernel<DQ, MV>;                                                              \
+    static bool attr = false;                                                                              \
+    if (!attr) { TI_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024)); attr = true; } \
+    k<<<grid, THREADS, smem, st>>>(p, stages);                                                             \
+  }
+  switch (maxv) {
+    case 1: TI_LNS(1); break;
+    case 2: TI_LNS(2); break;
+    case 4: TI_LNS(4); break;
+    default: TI_LNS(8); break;
+  }
+#undef TI_LNS
+  count_launch();
+  TI_CUDA_CHECK(cudaGetLastError());
+  return TI_OK;
+}
+
+// rows whose operands are contiguous fp32/int32 of a 16-byte multiple and fit the ring
+inline bool eligible(const ti_layernorm_params& g, bool vec_ok) {
+  if (!vec_ok || g.out_dtype != TI_I8 || g.param_dtype != TI_F32) return false;
+  if (g.x_dtype != TI_I32 && g.x_dtype != TI_F32) return false;
+  if (g.n > 6144 || g.n < 1024 || g.rows < 256) return false;
+  if (((uintptr_t)g.x & 15) || (g.x_row_stride % 4) != 0) return false;
+  return true;
+}
+
+}  // namespace stream
+
 inline int pick_tpr(int64_t n, int* maxv, int per_thread = 16) {
   // about `per_thread` elements per thread, 32..512 threads per row
   int tpr = 32;
@@ -336,6 +558,12 @@ inline int launch_layernorm(const ti_layernorm_params& g) {
                 aligned(g.gamma, 4 * ps) && aligned(g.beta, 4 * ps) && aligned(g.skip, 4 * ps) &&
                 aligned(g.residual_in, 16) && aligned(g.residual_out, 16) && aligned(g.bias_i32, 16);
 
+  if (stream::eligible(g, vec_ok)) {
+    int dev = 0, sms = 0;
+    TI_CUDA_CHECK(cudaGetDevice(&dev));
+    TI_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    return is_dq ? stream::launch<true>(p, sms, (cudaStream_t)g.stream) : stream::launch<false>(p, sms, (cudaStream_t)g.stream);
+  }
 #define TI_LN_DISPATCH(XT, PT)                                                   \
   return qout ? launch_ln_typed<XT, PT, true>(g, p, vec_ok) : launch_ln_typed<XT, PT, false>(g, p, vec_ok)
   if (is_dq) { TI_LN_DISPATCH(int32_t, float); }
