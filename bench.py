@@ -42,6 +42,8 @@ def parse():
     ap.add_argument("--small", action="store_true", help="reduced shapes (profiling under ncu)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--tp-mode", default="fused", choices=["fused", "nccl"],
+                    help="N>1: 'fused' = peer-memory reduce+LayerNorm+gather kernel, 'nccl' = int32 all-reduce then LayerNorm")
     return ap.parse_args()
 
 
@@ -193,6 +195,27 @@ def run_b200(args):
     acc_h = p["prev_acc"].pin_memory()
     residual, prev_acc = residual_h.to(dev), acc_h.to(dev)
     del p
+    tp_mode = "single" if world == 1 else args.tp_mode
+    bufs = None
+    if tp_mode == "fused":
+        # residual stream row-sharded; the int32 partial sums and the gathered int8
+        # activations live in peer-mapped buffers
+        from triton_int_b200 import tp
+        try:
+            bufs = tp.SymmetricBuffers(dist.group.WORLD, tokens, cfg["hidden"], dev)
+        except Exception as exc:  # symmetric memory not available on this box
+            if rank == 0:
+                print(f"[bench] symmetric memory unavailable ({exc}); using the NCCL all-reduce path", file=sys.stderr)
+            tp_mode = "nccl"
+    if tp_mode == "fused":
+        r0, rc = bufs.rank_rows()
+        state = {"res": residual[r0:r0 + rc].contiguous()}
+        if rank == 0:
+            bufs.partial[0][0].copy_(prev_acc)   # the previous block's partial sums: all on rank 0 here
+        else:
+            bufs.partial[0][0].zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
 
     # ---- per-launch timing of the dominant kernel: wrap the GEMM launcher with events
     gemm_events = []
@@ -215,6 +238,11 @@ def run_b200(args):
     KF.gemm = timed_gemm
 
     def step():
+        if tp_mode == "fused":
+            # chained like a stack of blocks: the fc2 partial sums left in the peer-mapped
+            # buffer are the next step's input, the residual shard carries over
+            state["res"] = block.forward_tp_fused(state["res"], bufs, cfg["batch"], cfg["seq"])
+            return state["res"]
         return block(residual, prev_acc, cfg["batch"], cfg["seq"])
 
     def barrier():
@@ -254,7 +282,7 @@ def run_b200(args):
 
     # ---- end to end from host buffers: H2D inputs, block, D2H outputs, three streams
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e:  # (host-buffer run uses the all-reduce form of the step at every N)
         e2e = run_e2e(block, residual_h, acc_h, cfg, dev, world, dist, max(3, args.steps // 2), barrier)
 
     if rank != 0:
@@ -273,7 +301,7 @@ def run_b200(args):
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": "configs[3]: OPT-6.7B-shape int8 decoder block, hidden 4096, 32 heads, FFN 16384, "
                                f"batch {cfg['batch']} x seq {cfg['seq']} = {tokens} tokens per step",
-                   "parallelism": f"tp{world}", "global_batch": cfg["batch"], "seq_len": cfg["seq"],
+                   "parallelism": f"tp{world}", "tp_exchange": tp_mode, "global_batch": cfg["batch"], "seq_len": cfg["seq"],
                    "l2": "working set (>= 5 GB of activations, 201 MB of weights) exceeds the 126 MB L2; no flush",
                    "rounding": "rne_sat"},
         "clocks": clocks,

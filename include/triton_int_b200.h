@@ -163,6 +163,38 @@ typedef struct {
 
 int ti_attention_i8(const ti_attention_params* p);
 
+/*
+ * Tensor-parallel exchange fused with its consumer, one launch per rank:
+ *   sum over ranks of the int32 partial sums of a row-parallel linear (read from
+ *   every rank's buffer with peer loads) + int32 bias -> dequantise -> + residual
+ *   -> LayerNorm -> int8, the int8 row stored into every rank's activation buffer.
+ * Rank r processes rows [row_begin, row_begin + row_count) of the [rows, n] matrix;
+ * residual_in / residual_out hold only those rows.  parts[i] / outs[i] are rank i's
+ * buffers as mapped into this process (peer-accessible device memory); entries at
+ * index >= world are ignored.  The caller orders this launch after every rank's
+ * producer of parts and orders every rank's consumer of outs after it (a stream
+ * barrier).  The reference has no distributed code; the arithmetic is that of
+ * dq_add_layernorm_q (functional/fused.py:6-15) applied to the exact integer sum.
+ */
+typedef struct {
+  const int32_t* parts[8];
+  int8_t* outs[8];
+  const float* residual_in;
+  float* residual_out;         /* optional */
+  const int32_t* bias_i32;     /* optional [n] */
+  const float* gamma;
+  const float* beta;           /* optional */
+  const float* dq_scale_dev;   /* optional device scalar overriding dq_scale */
+  int64_t row_begin, row_count, n;
+  float eps;
+  float dq_scale;
+  int32_t world;
+  int32_t rounding;
+  void* stream;
+} ti_tp_reduce_ln_params;
+
+int ti_tp_reduce_layernorm_q(const ti_tp_reduce_ln_params* p);
+
 /* Reads and clears the device-side status word of the current device.  Non-zero
  * means a bounded wait inside a kernel expired (bit 0: TMA producer, bit 1: MMA
  * issuer, bit 2: epilogue).  Synchronises the device. */

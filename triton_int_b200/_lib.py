@@ -23,7 +23,7 @@ PATH_AUTO, PATH_TCGEN05, PATH_GENERIC = range(3)
 DTYPE_CODE = {torch.int8: TI_I8, torch.int32: TI_I32, torch.float32: TI_F32,
               torch.float16: TI_F16, torch.bfloat16: TI_BF16}
 
-EXPORTS = ["ti_gemm_i8", "ti_layernorm", "ti_gelu_q", "ti_softmax_q", "ti_attention_i8", "ti_device_status",
+EXPORTS = ["ti_gemm_i8", "ti_layernorm", "ti_gelu_q", "ti_softmax_q", "ti_attention_i8", "ti_tp_reduce_layernorm_q", "ti_device_status",
            "ti_version", "ti_last_error_string", "ti_launch_count", "ti_device_supported"]
 
 
@@ -70,6 +70,17 @@ class AttentionParams(C.Structure):
     ]
 
 
+class TpReduceLnParams(C.Structure):
+    _fields_ = [
+        ("parts", C.c_void_p * 8), ("outs", C.c_void_p * 8),
+        ("residual_in", C.c_void_p), ("residual_out", C.c_void_p), ("bias_i32", C.c_void_p),
+        ("gamma", C.c_void_p), ("beta", C.c_void_p), ("dq_scale_dev", C.c_void_p),
+        ("row_begin", C.c_int64), ("row_count", C.c_int64), ("n", C.c_int64),
+        ("eps", C.c_float), ("dq_scale", C.c_float), ("world", C.c_int32), ("rounding", C.c_int32),
+        ("stream", C.c_void_p),
+    ]
+
+
 _LIB = None
 
 
@@ -95,6 +106,8 @@ def load():
     lib.ti_softmax_q.restype = C.c_int
     lib.ti_attention_i8.argtypes = [C.POINTER(AttentionParams)]
     lib.ti_attention_i8.restype = C.c_int
+    lib.ti_tp_reduce_layernorm_q.argtypes = [C.POINTER(TpReduceLnParams)]
+    lib.ti_tp_reduce_layernorm_q.restype = C.c_int
     lib.ti_device_status.argtypes = [C.POINTER(C.c_uint32)]
     lib.ti_device_status.restype = C.c_int
     lib.ti_version.restype = C.c_int

@@ -52,6 +52,7 @@ static int device_info(DeviceInfo* out) {
 #include "gemm_tcgen05.cuh"
 #include "rowwise.cuh"
 #include "attention_tcgen05.cuh"
+#include "tp_fused.cuh"
 
 using namespace ti;
 
@@ -193,6 +194,15 @@ int ti_attention_i8(const ti_attention_params* a) {
     return TI_ERR_DEVICE;
   }
   return ti::attn::launch(*a, di.sms);
+}
+
+int ti_tp_reduce_layernorm_q(const ti_tp_reduce_ln_params* p) {
+  if (!p) { set_error("tp: null params"); return TI_ERR_DEVICE; }
+  if (p->rounding != TI_ROUND_RNE_SAT && p->rounding != TI_ROUND_TRUNC_WRAP) { set_error("tp: bad rounding mode"); return TI_ERR_UNSUPPORTED; }
+  DeviceInfo di;
+  int rc = require_device(&di);
+  if (rc != TI_OK) return rc;
+  return ti::tp::launch(*p);
 }
 
 }  // extern "C"

@@ -122,3 +122,31 @@ class Int8DecoderBlock(torch.nn.Module):
         g8 = linear_a8_w8_bfp32_ofp32_GeLu_Q(h8, self.fc1_w, self.fc1_bias, self.fc1_alpha, self.fc1_mul)
         fc2_acc = self.reduce_fn(linear_a8_w8_b32_o32(g8, self.fc2_w, None))
         return res2, fc2_acc
+
+    @torch.no_grad()
+    def forward_tp_fused(self, residual_shard, bufs, batch, seq, prev_bias=None):
+        """Tensor-parallel step with the exchange fused into the LayerNorm kernels.
+
+        ``bufs`` is a ``triton_int_b200.tp.SymmetricBuffers``.  On entry ``bufs.partial[0]``
+        holds every rank's int32 partial sums of the previous block's fc2 and
+        ``residual_shard`` this rank's rows of the fp32 residual stream.  On return
+        ``bufs.partial[0]`` holds this block's fc2 partial sums (unreduced: the next
+        block's first kernel adds them) and the new residual shard is returned."""
+        from ..kernels._gemm import gemm
+        from .. import _lib, tp
+        rows = bufs.rank_rows()
+        (p0, p0_ptrs), (p1, p1_ptrs) = bufs.partial[0], bufs.partial[1]
+        (x8, x8_ptrs), (h8, h8_ptrs) = bufs.act[0], bufs.act[1]
+        bufs.barrier()  # every rank's partial sums in partial[0] are complete
+        res1 = tp.reduce_layernorm_q(p0_ptrs, x8_ptrs, rows, self.hidden, residual_shard, self.ln1_w, self.ln1_b,
+                                     self.eps, self.prev_scale, bias_int32=prev_bias)
+        bufs.barrier()  # x8 is complete everywhere; partial[0] may be overwritten
+        attn = self.attention(x8, batch, seq)
+        linear_a8_w8_b32_o32(attn, self.out_w, None, out=p1)
+        bufs.barrier()
+        res2 = tp.reduce_layernorm_q(p1_ptrs, h8_ptrs, rows, self.hidden, res1, self.ln2_w, self.ln2_b,
+                                     self.eps, self.out_scale, bias_int32=self.out_bias)
+        bufs.barrier()
+        g8 = linear_a8_w8_bfp32_ofp32_GeLu_Q(h8, self.fc1_w, self.fc1_bias, self.fc1_alpha, self.fc1_mul)
+        linear_a8_w8_b32_o32(g8, self.fc2_w, None, out=p0)
+        return res2
