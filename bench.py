@@ -44,6 +44,9 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--tp-mode", default="fused", choices=["fused", "nccl"],
                     help="N>1: 'fused' = peer-memory reduce+LayerNorm+gather kernel, 'nccl' = int32 all-reduce then LayerNorm")
+    ap.add_argument("--microbatches", type=int, default=2,
+                    help="N>1, fused exchange: sequences are split into this many groups that run on their own "
+                         "streams so one group's exchange overlaps the other's GEMMs")
     return ap.parse_args()
 
 
@@ -197,23 +200,32 @@ def run_b200(args):
     del p
     tp_mode = "single" if world == 1 else args.tp_mode
     bufs = None
+    nmb = 1
     if tp_mode == "fused":
         # residual stream row-sharded; the int32 partial sums and the gathered int8
-        # activations live in peer-mapped buffers
+        # activations live in peer-mapped buffers, one set per group of sequences
         from triton_int_b200 import tp
+        nmb = max(1, min(args.microbatches, cfg["batch"]))
+        while cfg["batch"] % nmb:
+            nmb -= 1
         try:
-            bufs = tp.SymmetricBuffers(dist.group.WORLD, tokens, cfg["hidden"], dev)
+            bufs = [tp.SymmetricBuffers(dist.group.WORLD, tokens // nmb, cfg["hidden"], dev) for _ in range(nmb)]
         except Exception as exc:  # symmetric memory not available on this box
             if rank == 0:
                 print(f"[bench] symmetric memory unavailable ({exc}); using the NCCL all-reduce path", file=sys.stderr)
             tp_mode = "nccl"
     if tp_mode == "fused":
-        r0, rc = bufs.rank_rows()
-        state = {"res": residual[r0:r0 + rc].contiguous()}
-        if rank == 0:
-            bufs.partial[0][0].copy_(prev_acc)   # the previous block's partial sums: all on rank 0 here
-        else:
-            bufs.partial[0][0].zero_()
+        mb_tokens = tokens // nmb
+        r0, rc = bufs[0].rank_rows()
+        state = []
+        for i in range(nmb):
+            lo = i * mb_tokens
+            state.append(residual[lo + r0:lo + r0 + rc].contiguous())
+            if rank == 0:
+                bufs[i].partial[0][0].copy_(prev_acc[lo:lo + mb_tokens])   # the previous block's partial sums: all on rank 0 here
+            else:
+                bufs[i].partial[0][0].zero_()
+        side = [torch.cuda.Stream(dev) for _ in range(nmb)]
         torch.cuda.synchronize()
         dist.barrier()
 
@@ -240,9 +252,16 @@ def run_b200(args):
     def step():
         if tp_mode == "fused":
             # chained like a stack of blocks: the fc2 partial sums left in the peer-mapped
-            # buffer are the next step's input, the residual shard carries over
-            state["res"] = block.forward_tp_fused(state["res"], bufs, cfg["batch"], cfg["seq"])
-            return state["res"]
+            # buffer are the next step's input, the residual shard carries over.  Each group
+            # of sequences runs on its own stream.
+            main = torch.cuda.current_stream(dev)
+            for i in range(nmb):
+                side[i].wait_stream(main)
+                with torch.cuda.stream(side[i]):
+                    state[i] = block.forward_tp_fused(state[i], bufs[i], cfg["batch"] // nmb, cfg["seq"])
+            for i in range(nmb):
+                main.wait_stream(side[i])
+            return state
         return block(residual, prev_acc, cfg["batch"], cfg["seq"])
 
     def barrier():
@@ -301,7 +320,7 @@ def run_b200(args):
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": "configs[3]: OPT-6.7B-shape int8 decoder block, hidden 4096, 32 heads, FFN 16384, "
                                f"batch {cfg['batch']} x seq {cfg['seq']} = {tokens} tokens per step",
-                   "parallelism": f"tp{world}", "tp_exchange": tp_mode, "global_batch": cfg["batch"], "seq_len": cfg["seq"],
+                   "parallelism": f"tp{world}", "tp_exchange": tp_mode, "microbatches": nmb, "global_batch": cfg["batch"], "seq_len": cfg["seq"],
                    "l2": "working set (>= 5 GB of activations, 201 MB of weights) exceeds the 126 MB L2; no flush",
                    "rounding": "rne_sat"},
         "clocks": clocks,

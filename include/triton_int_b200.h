@@ -195,6 +195,13 @@ typedef struct {
 
 int ti_tp_reduce_layernorm_q(const ti_tp_reduce_ln_params* p);
 
+/* Stream-ordered barrier between the `world` ranks of one node.  pads[i] is rank i's
+ * pad of 8 zero-initialised uint32 flags in peer-mapped memory, as mapped into this
+ * process.  `epoch` must increase by one on every call and be the same on every rank.
+ * The wait on the device is bounded (2 s); on expiry bit 3 of the status word is set.
+ * Part of the tensor-parallel plumbing; the reference has no counterpart. */
+int ti_tp_barrier(uint32_t* const* pads, int32_t world, int32_t rank, uint32_t epoch, void* stream);
+
 /* Reads and clears the device-side status word of the current device.  Non-zero
  * means a bounded wait inside a kernel expired (bit 0: TMA producer, bit 1: MMA
  * issuer, bit 2: epilogue).  Synchronises the device. */

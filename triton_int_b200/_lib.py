@@ -23,7 +23,7 @@ PATH_AUTO, PATH_TCGEN05, PATH_GENERIC = range(3)
 DTYPE_CODE = {torch.int8: TI_I8, torch.int32: TI_I32, torch.float32: TI_F32,
               torch.float16: TI_F16, torch.bfloat16: TI_BF16}
 
-EXPORTS = ["ti_gemm_i8", "ti_layernorm", "ti_gelu_q", "ti_softmax_q", "ti_attention_i8", "ti_tp_reduce_layernorm_q", "ti_device_status",
+EXPORTS = ["ti_gemm_i8", "ti_layernorm", "ti_gelu_q", "ti_softmax_q", "ti_attention_i8", "ti_tp_reduce_layernorm_q", "ti_tp_barrier", "ti_device_status",
            "ti_version", "ti_last_error_string", "ti_launch_count", "ti_device_supported"]
 
 
@@ -108,6 +108,8 @@ def load():
     lib.ti_attention_i8.restype = C.c_int
     lib.ti_tp_reduce_layernorm_q.argtypes = [C.POINTER(TpReduceLnParams)]
     lib.ti_tp_reduce_layernorm_q.restype = C.c_int
+    lib.ti_tp_barrier.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_uint32, C.c_void_p]
+    lib.ti_tp_barrier.restype = C.c_int
     lib.ti_device_status.argtypes = [C.POINTER(C.c_uint32)]
     lib.ti_device_status.restype = C.c_int
     lib.ti_version.restype = C.c_int

@@ -113,6 +113,56 @@ tp_reduce_layernorm_q_kernel(const Params p, const int tpr) {
   }
 }
 
+// Device-side barrier between the ranks of one node, ordered on a stream.  Every rank
+// owns a pad of MAX_WORLD 32-bit flags in peer-mapped memory; rank r stores the epoch
+// number into flag r of every rank's pad (system-scope release) and then waits until
+// all flags of its own pad have reached the epoch (system-scope acquire).  The wait is
+// bounded: after the limit the kernel records STATUS_TP_PEER and returns.
+struct BarrierParams {
+  uint32_t* pads[MAX_WORLD];
+  int world, rank;
+  uint32_t epoch;
+};
+__global__ void tp_barrier_kernel(const BarrierParams p) {
+  const int q = threadIdx.x;
+  if (q >= p.world) return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.pads[q] + p.rank), "r"(p.epoch) : "memory");
+  const uint32_t* mine = p.pads[p.rank] + q;
+  uint64_t t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  uint32_t spins = 0;
+  for (;;) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if ((int32_t)(v - p.epoch) >= 0) break;
+    if ((++spins & 63u) == 0u) {
+      uint64_t t1;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+      if (t1 - t0 > 2000000000ull) {
+        atomicOr(&g_status, STATUS_TP_PEER);
+        break;
+      }
+    }
+  }
+  __threadfence_system();
+}
+
+inline int launch_barrier(uint32_t* const* pads, int world, int rank, uint32_t epoch, void* stream) {
+  if (world < 1 || world > MAX_WORLD || rank < 0 || rank >= world) { set_error("tp barrier: bad world/rank"); return TI_ERR_UNSUPPORTED; }
+  BarrierParams p;
+  for (int r = 0; r < MAX_WORLD; ++r) p.pads[r] = nullptr;
+  for (int r = 0; r < world; ++r) {
+    if (!pads[r] || ((uintptr_t)pads[r] & 3)) { set_error("tp barrier: null or misaligned pad for rank %d", r); return TI_ERR_ALIGN; }
+    p.pads[r] = pads[r];
+  }
+  p.world = world; p.rank = rank; p.epoch = epoch;
+  tp_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(p);
+  count_launch();
+  TI_CUDA_CHECK(cudaGetLastError());
+  return TI_OK;
+}
+
 inline int launch(const ti_tp_reduce_ln_params& g) {
   if (g.world < 1 || g.world > MAX_WORLD) { set_error("tp: world size must be 1..8"); return TI_ERR_UNSUPPORTED; }
   if (g.row_count < 0 || g.n <= 0 || g.row_begin < 0) { set_error("tp: bad extents"); return TI_ERR_SHAPE; }

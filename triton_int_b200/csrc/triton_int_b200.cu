@@ -205,4 +205,12 @@ int ti_tp_reduce_layernorm_q(const ti_tp_reduce_ln_params* p) {
   return ti::tp::launch(*p);
 }
 
+int ti_tp_barrier(uint32_t* const* pads, int32_t world, int32_t rank, uint32_t epoch, void* stream) {
+  if (!pads) { set_error("tp barrier: null pads"); return TI_ERR_DEVICE; }
+  DeviceInfo di;
+  int rc = require_device(&di);
+  if (rc != TI_OK) return rc;
+  return ti::tp::launch_barrier(pads, world, rank, epoch, stream);
+}
+
 }  // extern "C"

@@ -85,16 +85,26 @@ class SymmetricBuffers:
             h = symm.rendezvous(t, group)
             self.act.append((t, [int(x) for x in h.buffer_ptrs]))
             self._handles.append(h)
-        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
-        self._dist = dist
+        # pad of flags for this library's own bounded barrier
+        pad = symm.empty((8,), dtype=torch.int32, device=device)
+        pad.zero_()
+        ph = symm.rendezvous(pad, group)
+        self._pad, self._pad_ptrs = pad, (C.c_void_p * 8)(*[int(x) for x in ph.buffer_ptrs])
+        self._handles.append(ph)
+        self._epoch = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # every pad is zeroed before anyone's first device barrier
 
     def rank_rows(self):
         per = self.rows // self.world
         return self.rank * per, per
 
     def barrier(self):
-        """All ranks' streams have reached this point before any proceeds."""
-        try:
-            self._handles[0].barrier()
-        except Exception:
-            self._dist.all_reduce(self._flag, group=self.group)
+        """All ranks' streams have reached this point before any proceeds (bounded wait on
+        the device; an expired wait shows up in ``triton_int_b200.device_status()``)."""
+        self._epoch += 1
+        dev = self._pad.device
+        with torch.cuda.device(dev):
+            rc = _lib.load().ti_tp_barrier(self._pad_ptrs, self.world, self.rank, self._epoch & 0xFFFFFFFF,
+                                           _lib.current_stream_ptr(dev))
+        _lib.check(rc, "ti_tp_barrier")
