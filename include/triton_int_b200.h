@@ -75,7 +75,17 @@ typedef struct {
   int32_t path;            /* ti_gemm_path */
   int32_t causal;          /* 1: skip output tiles with n0 > m0 + BM - 1 + (n - m) (never read by a causal softmax) */
   void* stream;            /* cudaStream_t */
+  /* Optional scratch for split-K (few output tiles, long K: the M <= 128 weight-streaming
+   * shapes).  When workspace_bytes >= ti_gemm_workspace_bytes(p) the K range is divided
+   * over several CTAs per tile, int32 partial sums go to the workspace and a second
+   * kernel adds them (exactly) and applies the epilogue.  NULL / 0: never split. */
+  void* workspace;
+  int64_t workspace_bytes;
 } ti_gemm_params;
+
+/* Bytes of workspace with which ti_gemm_i8 would split K for this problem on the
+ * current device; 0 when it would not split. */
+int64_t ti_gemm_workspace_bytes(const ti_gemm_params* p);
 
 int ti_gemm_i8(const ti_gemm_params* p);
 

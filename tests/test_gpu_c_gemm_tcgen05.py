@@ -154,3 +154,24 @@ def test_full_size_properties():
         a1 = KL.linear_a8_w8_b32_o32(dev(x1), wd, None)
         a2 = KL.linear_a8_w8_b32_o32(dev(x2), wd, None)
     assert torch.equal(a1 + a2, acc)
+
+
+@pytest.mark.parametrize("m", [1, 16, 128])
+def test_split_k_small_m(m):
+    """Config-5 weight-streaming shapes: K is split over CTAs, partial sums meet in a scratch
+    buffer and the second kernel applies the epilogue; results equal the oracle."""
+    from triton_int_b200 import _lib
+    c = synthetic.config5_linear(seed=4, m=m, layer="fc1")
+    x, w = c["x"], c["w"]
+    with gemm_path("tcgen05"):
+        before = _lib.launch_count()
+        acc = KL.linear_a8_w8_b32_o32(dev(x), dev(w), None)
+        assert _lib.launch_count() - before == 2, "expected the two-kernel split-K form"
+        y8 = KL.linear_a8_w8_b8_o8(dev(x), dev(w), dev(c["bias_i8"]), dev(c["alpha"]), dev(c["beta"]))
+        yf = KL.linear_a8_w8_bfp32_ofp32(dev(x), dev(w), dev(c["bias_f32"]), dev(c["alpha"]), dev(c["beta"]))
+        yg = KF.linear_a8_w8_bfp32_ofp32_GeLu_Q(dev(x), dev(w), dev(c["bias_f32"]), dev(c["alpha"]), torch.tensor(50.0).cuda())
+    assert_status_clean()
+    assert_equal(acc, O.acc_linear(x, w), "split-K accumulators")
+    assert_equal(y8, O.linear_a8_w8_b8_o8(x, w, c["bias_i8"], c["alpha"], c["beta"], O.RNE_SAT), "split-K b8_o8")
+    assert_equal(yf, O.linear_a8_w8_bfp32_ofp32(x, w, c["bias_f32"], c["alpha"], c["beta"]), "split-K bfp32")
+    assert_within_1lsb(yg, O.linear_a8_w8_bfp32_ofp32_GeLu_Q(x, w, c["bias_f32"], c["alpha"], torch.tensor(50.0), O.RNE_SAT), 2e-3, "split-K gelu_q")

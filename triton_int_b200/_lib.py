@@ -23,7 +23,7 @@ PATH_AUTO, PATH_TCGEN05, PATH_GENERIC = range(3)
 DTYPE_CODE = {torch.int8: TI_I8, torch.int32: TI_I32, torch.float32: TI_F32,
               torch.float16: TI_F16, torch.bfloat16: TI_BF16}
 
-EXPORTS = ["ti_gemm_i8", "ti_layernorm", "ti_gelu_q", "ti_softmax_q", "ti_attention_i8", "ti_tp_reduce_layernorm_q", "ti_tp_barrier", "ti_device_status",
+EXPORTS = ["ti_gemm_i8", "ti_gemm_workspace_bytes", "ti_layernorm", "ti_gelu_q", "ti_softmax_q", "ti_attention_i8", "ti_tp_reduce_layernorm_q", "ti_tp_barrier", "ti_device_status",
            "ti_version", "ti_last_error_string", "ti_launch_count", "ti_device_supported"]
 
 
@@ -38,6 +38,7 @@ class GemmParams(C.Structure):
         ("bias_dtype", C.c_int32), ("out_dtype", C.c_int32), ("epilogue", C.c_int32),
         ("rounding", C.c_int32), ("path", C.c_int32), ("causal", C.c_int32),
         ("stream", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
     ]
 
 
@@ -98,6 +99,8 @@ def load():
     lib = C.CDLL(_build.LIB_PATH)
     lib.ti_gemm_i8.argtypes = [C.POINTER(GemmParams)]
     lib.ti_gemm_i8.restype = C.c_int
+    lib.ti_gemm_workspace_bytes.argtypes = [C.POINTER(GemmParams)]
+    lib.ti_gemm_workspace_bytes.restype = C.c_int64
     lib.ti_layernorm.argtypes = [C.POINTER(LayerNormParams)]
     lib.ti_layernorm.restype = C.c_int
     lib.ti_gelu_q.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_float, C.c_int32, C.c_void_p]

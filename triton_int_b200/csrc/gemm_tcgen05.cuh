@@ -728,7 +728,125 @@ int launch_epi(const ti_gemm_params& g, int num_sms) {
   return launch_cfg<64, 8, OutT, EPI>(g, num_sms);
 }
 
+// ------------------------------------------------------------------ split-K
+// Second step of a split-K GEMM: out = epilogue(sum_s ws[s][m][n]).  The int32 sum is
+// exact in any order; the epilogue arithmetic is the one of the fused epilogue.
+struct ReduceParams {
+  const int32_t* ws;
+  void* c;
+  const void* bias;
+  const float* alpha;
+  const float* beta;
+  int64_t m, n, c_stride_m, c_stride_n;
+  int splits, bias_dtype, epilogue, rounding;
+};
+
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const ReduceParams p) {
+  const int64_t quads = p.n >> 2;  // n is a multiple of 4 on this path
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= p.m * quads) return;
+  const int64_t row = idx / quads;
+  const int64_t col = (idx - row * quads) << 2;
+  const int64_t plane = p.m * p.n;
+  const int32_t* src = p.ws + row * p.n + col;
+  int4 a = make_int4(0, 0, 0, 0);
+  for (int s = 0; s < p.splits; ++s) {
+    const int4 v = __ldcs(reinterpret_cast<const int4*>(src + (int64_t)s * plane));
+    a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+  }
+  const int32_t acc[4] = {a.x, a.y, a.z, a.w};
+  const float alpha = p.alpha ? *p.alpha : 1.0f;
+  const float beta = p.beta ? *p.beta : 1.0f;
+  OutT* dst = reinterpret_cast<OutT*>(p.c) + row * p.c_stride_m + col * p.c_stride_n;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    OutT o;
+    if (p.epilogue == TI_EPI_I32) {
+      int32_t v = acc[j];
+      if (p.bias) v += ((const int32_t*)p.bias)[col + j];
+      if constexpr (sizeof(OutT) == 4) *reinterpret_cast<int32_t*>(&o) = v; else o = OutT();
+    } else {
+      const float b = p.bias ? load_bias_f32(p.bias, p.bias_dtype, col + j) : 0.f;
+      float f;
+      if (p.epilogue == TI_EPI_GELU_Q) {
+        f = gelu_q_fast(__fadd_rn(__fmul_rn(__int2float_rn(acc[j]), alpha), b), beta);
+      } else {
+        f = epilogue_f32(acc[j], b, alpha, beta, p.epilogue);
+      }
+      o = OutCast<OutT>::from(f, p.rounding);
+      if constexpr (sizeof(OutT) == 1) {
+        if (p.epilogue == TI_EPI_SCALE_BIAS_RELU) o = o < 0 ? (OutT)0 : o;
+      }
+    }
+    dst[j * p.c_stride_n] = o;
+  }
+}
+
+// How many ways to split K: only for single (non-batched) problems whose tiles leave more
+// than half of the SMs idle, K at least 8 stages long, N a multiple of 4.  The split count
+// divides the number of 128-byte K blocks so every part is whole.
+inline int pick_splits(const ti_gemm_params& g, int num_sms) {
+  if (g.batch != 1 || g.causal || (g.n % 4) != 0 || (g.k % BK) != 0) return 1;
+  const int bn = g.n > 128 ? 256 : (g.n > 64 ? 128 : 64);
+  const int64_t tiles = ((g.m + BM - 1) / BM) * ((g.n + bn - 1) / bn);
+  const int64_t kb = g.k / BK;
+  if (tiles * 2 > num_sms || kb < 8) return 1;
+  int best = 1;
+  for (int s = 2; s <= 32; ++s)
+    if (kb % s == 0 && kb / s >= 2 && tiles * s <= num_sms) best = s;
+  return best;
+}
+
+inline int64_t workspace_bytes(const ti_gemm_params& g, int num_sms) {
+  if (!eligible(g)) return 0;
+  const int s = pick_splits(g, num_sms);
+  return s > 1 ? (int64_t)s * g.m * g.n * 4 : 0;
+}
+
+inline int launch_plain(const ti_gemm_params& g, int num_sms);
+
 inline int launch(const ti_gemm_params& g, int num_sms) {
+  const int splits = pick_splits(g, num_sms);
+  const int64_t need = splits > 1 ? (int64_t)splits * g.m * g.n * 4 : 0;
+  if (splits <= 1 || !g.workspace || g.workspace_bytes < need || ((uintptr_t)g.workspace & 15)) return launch_plain(g, num_sms);
+  // step 1: the K parts as a batched GEMM into the workspace (raw int32 accumulators)
+  ti_gemm_params part = g;
+  const int64_t ks = g.k / splits;
+  part.k = ks;
+  part.batch = splits;
+  part.a_stride_batch = ks;   // part s starts ks elements further along K
+  part.b_stride_batch = ks;
+  part.c = g.workspace;
+  part.c_stride_m = g.n; part.c_stride_n = 1; part.c_stride_batch = g.m * g.n;
+  part.bias = nullptr; part.alpha = nullptr; part.beta = nullptr;
+  part.out_dtype = TI_I32; part.epilogue = TI_EPI_I32;
+  part.workspace = nullptr; part.workspace_bytes = 0;
+  int rc = launch_plain(part, num_sms);
+  if (rc != TI_OK) return launch_plain(g, num_sms);  // (a driver that refuses the K-part view: unsplit)
+  // step 2: exact sum + epilogue
+  ReduceParams r;
+  r.ws = (const int32_t*)g.workspace; r.c = g.c; r.bias = g.bias; r.alpha = g.alpha; r.beta = g.beta;
+  r.m = g.m; r.n = g.n; r.c_stride_m = g.c_stride_m; r.c_stride_n = g.c_stride_n;
+  r.splits = splits; r.bias_dtype = g.bias_dtype; r.epilogue = g.epilogue; r.rounding = g.rounding;
+  const int64_t threads = g.m * (g.n >> 2);
+  const unsigned grid = (unsigned)((threads + 255) / 256);
+  cudaStream_t st = (cudaStream_t)g.stream;
+  switch (g.out_dtype) {
+    case TI_I8: splitk_reduce_kernel<int8_t><<<grid, 256, 0, st>>>(r); break;
+    case TI_I32: splitk_reduce_kernel<int32_t><<<grid, 256, 0, st>>>(r); break;
+    case TI_F32: splitk_reduce_kernel<float><<<grid, 256, 0, st>>>(r); break;
+    case TI_F16: splitk_reduce_kernel<__half><<<grid, 256, 0, st>>>(r); break;
+    case TI_BF16: splitk_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(r); break;
+    default: set_error("unsupported output dtype %d", g.out_dtype); return TI_ERR_DTYPE;
+  }
+  count_launch();
+  TI_CUDA_CHECK(cudaGetLastError());
+  return TI_OK;
+}
+
+inline int launch_plain(const ti_gemm_params& g, int num_sms) {
   const int ep = g.epilogue;
   switch (g.out_dtype) {
     case TI_I8:

@@ -139,6 +139,14 @@ int ti_gemm_i8(const ti_gemm_params* g) {
   return fast ? ti::tc::launch(*g, di.sms) : ti::generic::launch(*g);
 }
 
+int64_t ti_gemm_workspace_bytes(const ti_gemm_params* g) {
+  if (!g) return 0;
+  DeviceInfo di;
+  if (device_info(&di) != TI_OK || !di.ok) return 0;
+  if (g->path == TI_PATH_GENERIC) return 0;
+  return ti::tc::workspace_bytes(*g, di.sms);
+}
+
 int ti_layernorm(const ti_layernorm_params* p) {
   if (!p) { set_error("layernorm: null params"); return TI_ERR_DEVICE; }
   DeviceInfo di;

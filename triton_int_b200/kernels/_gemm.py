@@ -82,6 +82,13 @@ def gemm(a3, b3, b_is_nk, out_dtype, epilogue, *, bias=None, alpha=None, beta=No
     p.causal = 1 if causal else 0
     with torch.cuda.device(dev):
         p.stream = _lib.current_stream_ptr(dev)
+        if B == 1 and M <= 256:
+            # few output tiles: let the library split K; the scratch comes from torch's allocator
+            need = lib.ti_gemm_workspace_bytes(C.byref(p))
+            if need > 0:
+                ws = torch.empty(need, dtype=torch.uint8, device=dev)
+                keep.append(ws)
+                p.workspace, p.workspace_bytes = ws.data_ptr(), need
         rc = lib.ti_gemm_i8(C.byref(p))
     _lib.check(rc, "ti_gemm_i8")
     return c

@@ -56,6 +56,33 @@ def timeit(fn, iters, warm=3, flush=False):
     return ts[len(ts) // 2]
 
 
+def timeit_graph(fn, iters, calls=20):
+    """Device time per call with the host out of the picture: `calls` launches are captured
+    into one CUDA graph and the graph is replayed (small problems finish faster than Python
+    can issue them)."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(calls):
+                fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        graph.replay()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e) / calls)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
 def emit(op, shape, ms, ops=None, nbytes=None, **extra):
     line = {"op": op, "shape": shape, "ms": round(ms, 5)}
     if ops is not None:
@@ -69,7 +96,7 @@ def emit(op, shape, ms, ops=None, nbytes=None, **extra):
     print(json.dumps(line), flush=True)
 
 
-def bench_linear(m, n, k, iters, epilogues=("i32", "b8o8", "f32", "geluq"), cublas=True):
+def bench_linear(m, n, k, iters, epilogues=("i32", "b8o8", "f32", "geluq"), cublas=True, graph=False):
     g = synthetic.gen(4)
     x, w = synthetic.int8_normal((m, k), 35, g).cuda(), synthetic.int8_normal((n, k), 35, g).cuda()
     b8, bf = synthetic.int8_normal((n,), 35, g).cuda(), torch.randn((n,), generator=g).cuda()
@@ -79,7 +106,12 @@ def bench_linear(m, n, k, iters, epilogues=("i32", "b8o8", "f32", "geluq"), cubl
            "f32": lambda: KL.linear_a8_w8_bfp32_ofp32(x, w, bf, a, b),
            "geluq": lambda: KF.linear_a8_w8_bfp32_ofp32_GeLu_Q(x, w, bf, a, torch.tensor(50.0).cuda())}
     for name in epilogues:
-        emit(f"linear_{name}", [m, n, k], timeit(fns[name], iters), ops=2 * m * n * k)
+        if graph:
+            out_bytes = m * n * (1 if name in ("b8o8", "geluq") else 4)
+            emit(f"linear_{name}", [m, n, k], timeit_graph(fns[name], iters), ops=2 * m * n * k,
+                 nbytes=m * k + n * k + out_bytes, timing="cuda graph replay (device time per call)")
+        else:
+            emit(f"linear_{name}", [m, n, k], timeit(fns[name], iters), ops=2 * m * n * k)
     if cublas and m > 16 and m % 8 == 0 and n % 8 == 0 and k % 8 == 0:
         emit("cublaslt_int_mm (torch._int_mm, for comparison)", [m, n, k],
              timeit(lambda: torch._int_mm(x, w.t()), iters), ops=2 * m * n * k)
@@ -160,7 +192,7 @@ def main():
         for layer in ("fc1", "fc2", "qkv"):
             n, k = {"fc1": (4608, 9216), "fc2": (9216, 4608), "qkv": (3456, 9216)}[layer]
             for m in (1, 16, 128, 1024, 4096, 16384):
-                bench_linear(m, n, k, args.iters, ("b8o8", "f32"), cublas=False)
+                bench_linear(m, n, k, args.iters, ("b8o8", "f32"), cublas=False, graph=(m <= 1024))
     st = _lib.device_status()
     if st:
         raise SystemExit(f"device status {st:#x}")
