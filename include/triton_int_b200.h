@@ -90,6 +90,32 @@ int64_t ti_gemm_workspace_bytes(const ti_gemm_params* p);
 int ti_gemm_i8(const ti_gemm_params* p);
 
 /*
+ * ti_gemm_i8 for callers that cannot hand over (or obtain) device memory.
+ *
+ * Some hosts of this library must not call cudaMalloc on the hot path: a serving
+ * process that reserved the whole HBM for its own pools at start-up (a later
+ * cudaMalloc simply fails), a latency-critical loop (cudaMalloc synchronises the whole
+ * device), or a plugin that is not allowed to own device memory.  Without scratch,
+ * ti_gemm_i8 runs small-M problems unsplit and leaves most SMs idle.  This variant
+ * takes the same struct, ignores its workspace fields and, when the problem would
+ * split K, keeps the int32 partial sums in an array that is part of the library image
+ * (ti_static_scratch_bytes() bytes, 8 MiB: enough for M up to about 48 rows of the
+ * config-5 layers; every GPU that loads the library holds it
+ * until the process exits).  It calls no allocator of any kind.
+ *   - Problems whose partial sums need more than that are refused with
+ *     TI_ERR_UNSUPPORTED and a message naming both sizes.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call, with the device current, before
+ *     any stream capture begins.
+ *   - All calls on a device share the one array: two calls whose kernels can overlap on
+ *     the GPU (different streams) race on it.  Serialise them on one stream.  Nothing in
+ *     the array needs to start at zero: every partial sum a call reads, it wrote itself.
+ * It has no counterpart in the reference.
+ */
+int ti_gemm_i8_static_scratch(const ti_gemm_params* p);
+int64_t ti_static_scratch_bytes(void);
+
+/*
  * Row-wise normalisation family.  One struct covers
  *   layer_norm_fwd_fused_single_pass_q      kernels/fused.py:235-382   (out int8)
  *   layer_norm_fwd_fused_single_pass        kernels/fused.py:385-532   (out = input dtype)

@@ -23,7 +23,7 @@ PATH_AUTO, PATH_TCGEN05, PATH_GENERIC = range(3)
 DTYPE_CODE = {torch.int8: TI_I8, torch.int32: TI_I32, torch.float32: TI_F32,
               torch.float16: TI_F16, torch.bfloat16: TI_BF16}
 
-EXPORTS = ["ti_gemm_i8", "ti_gemm_workspace_bytes", "ti_layernorm", "ti_gelu_q", "ti_softmax_q", "ti_attention_i8", "ti_tp_reduce_layernorm_q", "ti_tp_barrier", "ti_device_status",
+EXPORTS = ["ti_gemm_i8", "ti_gemm_workspace_bytes", "ti_gemm_i8_static_scratch", "ti_static_scratch_bytes", "ti_layernorm", "ti_gelu_q", "ti_softmax_q", "ti_attention_i8", "ti_tp_reduce_layernorm_q", "ti_tp_barrier", "ti_device_status",
            "ti_version", "ti_last_error_string", "ti_launch_count", "ti_device_supported"]
 
 
@@ -99,6 +99,9 @@ def load():
     lib = C.CDLL(_build.LIB_PATH)
     lib.ti_gemm_i8.argtypes = [C.POINTER(GemmParams)]
     lib.ti_gemm_i8.restype = C.c_int
+    lib.ti_gemm_i8_static_scratch.argtypes = [C.POINTER(GemmParams)]
+    lib.ti_gemm_i8_static_scratch.restype = C.c_int
+    lib.ti_static_scratch_bytes.restype = C.c_int64
     lib.ti_gemm_workspace_bytes.argtypes = [C.POINTER(GemmParams)]
     lib.ti_gemm_workspace_bytes.restype = C.c_int64
     lib.ti_layernorm.argtypes = [C.POINTER(LayerNormParams)]

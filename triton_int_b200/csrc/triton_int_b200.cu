@@ -139,6 +139,57 @@ int ti_gemm_i8(const ti_gemm_params* g) {
   return fast ? ti::tc::launch(*g, di.sms) : ti::generic::launch(*g);
 }
 
+// ---------------------------------------------------------------------------
+// Split-K scratch that lives inside the library image, for ti_gemm_i8_static_scratch.
+// The name below is only a host-side handle for the symbol; the device address is
+// looked up once per device with cudaGetSymbolAddress and that pointer is what the
+// kernels receive.
+#define TI_STATIC_SCRATCH_BYTES (8ll * 1024 * 1024)
+static __device__ __align__(256) unsigned char g_static_scratch[TI_STATIC_SCRATCH_BYTES];
+
+static int static_scratch_ptr(void** out) {
+  static void* per_device[64] = {nullptr};
+  int dev = -1;
+  TI_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) { set_error("static scratch: device index %d out of range", dev); return TI_ERR_DEVICE; }
+  if (!per_device[dev]) {
+    void* ptr = nullptr;
+    // resolves the symbol in the context of the CURRENT device (dev)
+    TI_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    if (!ptr) { set_error("static scratch: cudaGetSymbolAddress returned a null address"); return TI_ERR_CUDA; }
+    per_device[dev] = ptr;
+  }
+  *out = per_device[dev];
+  return TI_OK;
+}
+
+int64_t ti_static_scratch_bytes(void) { return TI_STATIC_SCRATCH_BYTES; }
+
+int ti_gemm_i8_static_scratch(const ti_gemm_params* g) {
+  if (!g) { set_error("gemm: null params"); return TI_ERR_DEVICE; }
+  DeviceInfo di;
+  int rc = require_device(&di);
+  if (rc != TI_OK) return rc;
+  ti_gemm_params local = *g;
+  local.workspace = nullptr;
+  local.workspace_bytes = 0;
+  const int64_t need = (g->path == TI_PATH_GENERIC) ? 0 : ti::tc::workspace_bytes(local, di.sms);
+  if (need > TI_STATIC_SCRATCH_BYTES) {
+    set_error("gemm (static scratch): this problem splits K into partial sums of %lld bytes, the built-in scratch holds %lld; "
+              "use ti_gemm_i8 with a caller-provided workspace, or without one (unsplit)",
+              (long long)need, (long long)TI_STATIC_SCRATCH_BYTES);
+    return TI_ERR_UNSUPPORTED;
+  }
+  if (need > 0) {
+    void* ptr = nullptr;
+    rc = static_scratch_ptr(&ptr);
+    if (rc != TI_OK) return rc;
+    local.workspace = ptr;
+    local.workspace_bytes = TI_STATIC_SCRATCH_BYTES;
+  }
+  return ti_gemm_i8(&local);
+}
+
 int64_t ti_gemm_workspace_bytes(const ti_gemm_params* g) {
   if (!g) return 0;
   DeviceInfo di;
