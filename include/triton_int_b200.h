@@ -222,14 +222,38 @@ typedef struct {
   const float* beta;           /* optional */
   const float* dq_scale_dev;   /* optional device scalar overriding dq_scale */
   int64_t row_begin, row_count, n;
+  int64_t parts_row_begin;     /* row of parts[i] that holds matrix row row_begin (row_begin for full-size
+                                  buffers, 0 for receive slots that only hold this rank's rows) */
   float eps;
   float dq_scale;
   int32_t world;
+  int32_t rank;                /* this process's rank: sets the order in which peers are visited */
   int32_t rounding;
   void* stream;
 } ti_tp_reduce_ln_params;
 
 int ti_tp_reduce_layernorm_q(const ti_tp_reduce_ln_params* p);
+
+/*
+ * Row-parallel linear fused with the first half of its reduce-scatter: the raw int32
+ * accumulators acc = A . B^T (no bias, no scaling; p->c, bias, alpha, beta are ignored)
+ * are not written to a local [m, n] matrix but, tile by tile as they finish, into the
+ * receive buffer of the rank that owns the tile's rows:
+ *     recv[owner][rank][row - owner * rows_per_rank][col],  owner = row / rows_per_rank
+ * recv[i] is rank i's buffer of world * rows_per_rank * n int32 as mapped into this
+ * process (peer-accessible memory).  The stores are TMA tensor stores issued from the
+ * GEMM's epilogue, so the NVLink traffic overlaps the remaining tiles' MMAs.  After a
+ * barrier, ti_tp_reduce_layernorm_q with parts[s] = recv[rank] + s * rows_per_rank * n
+ * adds the world slices locally.  The reference has no distributed code.
+ */
+typedef struct {
+  int32_t* recv[8];
+  int32_t world;
+  int32_t rank;
+  int64_t rows_per_rank;   /* multiple of 128; world * rows_per_rank == m */
+} ti_gemm_scatter;
+
+int ti_gemm_i8_scatter(const ti_gemm_params* p, const ti_gemm_scatter* sc);
 
 /* Stream-ordered barrier between the `world` ranks of one node.  pads[i] is rank i's
  * pad of 8 zero-initialised uint32 flags in peer-mapped memory, as mapped into this

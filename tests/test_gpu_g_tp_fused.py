@@ -34,3 +34,36 @@ def test_reduce_layernorm_q_matches_unfused(world, rows, n):
     for o in outs:  # every rank's copy of the gathered rows
         assert torch.equal(o, y_ref)
     assert_status_clean()
+
+
+@pytest.mark.parametrize("world,rows,n,k", [(2, 256, 512, 256), (4, 512, 4096, 1024)])
+def test_scatter_gemm_then_local_reduce(world, rows, n, k):
+    """Emulated ranks on one GPU: every rank's K-shard GEMM scatters its tiles into the owners'
+    receive buffers; each owner's reduce+LayerNorm over its slots equals the unsharded result."""
+    from oracle import ops as O
+    g = synthetic.gen(95 + world)
+    x = synthetic.int8_normal((rows, k), 40, g)
+    w = synthetic.int8_normal((n, k), 30, g)
+    per, ks = rows // world, k // world
+    recv = [torch.full((world, per, n), -5, dtype=torch.int32, device="cuda") for _ in range(world)]
+    ptrs = [t.data_ptr() for t in recv]
+    for r in range(world):
+        tp.gemm_scatter(x[:, r * ks:(r + 1) * ks].contiguous().cuda(), w[:, r * ks:(r + 1) * ks].contiguous().cuda(),
+                        ptrs, r, per)
+    torch.cuda.synchronize()
+    acc = O.acc_linear(x, w)
+    for owner in range(world):
+        total = recv[owner].sum(0, dtype=torch.int64).to(torch.int32)
+        assert torch.equal(total.cpu(), acc[owner * per:(owner + 1) * per]), f"owner {owner}"
+    residual = torch.randn((rows, n), generator=g).cuda()
+    gamma = (torch.rand((n,), generator=g) * 20 + 5).cuda()
+    outs = [torch.zeros((rows, n), dtype=torch.int8, device="cuda") for _ in range(world)]
+    for owner in range(world):
+        slots = [recv[owner][s].data_ptr() for s in range(world)]
+        tp.reduce_layernorm_q(slots, [o.data_ptr() for o in outs], (owner * per, per), n,
+                              residual[owner * per:(owner + 1) * per], gamma, None, 1e-5, 1e-4,
+                              parts_row_begin=0, rank=owner)
+    _, y_ref = KF.dq_add_layernorm_q(acc.cuda(), 1e-4, residual, gamma, None, 1e-5)
+    for o in outs:
+        assert torch.equal(o, y_ref)
+    assert_status_clean()

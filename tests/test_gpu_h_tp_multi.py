@@ -39,6 +39,18 @@ def _rank_main(rank, world, port, out):
     total = bufs.partial[0][0].clone()
     dist.all_reduce(total)  # sum of the fc2 partial sums
     ok = torch.equal(res, r_ref[r0:r0 + rc]) and torch.equal(total, a_ref)
+    # the push form: GEMM tiles scattered into the owners' receive buffers
+    bufs2 = tp.SymmetricBuffers(dist.group.WORLD, t, h, dev)
+    bufs2.partial[0][0].zero_()
+    if rank == 0:  # previous block's slices: everything in slot 0 of each owner
+        pass
+    bufs2.partial[0][0].view(world, rc, h)[0].copy_(p["prev_acc"].to(dev)[r0:r0 + rc])
+    torch.cuda.synchronize()
+    dist.barrier()
+    res_p = blk.forward_tp_push(p["residual"].to(dev)[r0:r0 + rc].contiguous(), bufs2, 2, 128)
+    bufs2.barrier()
+    mine = bufs2.partial[0][0].view(world, rc, h).sum(0, dtype=torch.int64).to(torch.int32)  # this rank's rows of fc2
+    ok = ok and torch.equal(res_p, r_ref[r0:r0 + rc]) and torch.equal(mine, a_ref[r0:r0 + rc])
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:

@@ -23,7 +23,7 @@ PATH_AUTO, PATH_TCGEN05, PATH_GENERIC = range(3)
 DTYPE_CODE = {torch.int8: TI_I8, torch.int32: TI_I32, torch.float32: TI_F32,
               torch.float16: TI_F16, torch.bfloat16: TI_BF16}
 
-EXPORTS = ["ti_gemm_i8", "ti_gemm_workspace_bytes", "ti_gemm_i8_static_scratch", "ti_static_scratch_bytes", "ti_layernorm", "ti_gelu_q", "ti_softmax_q", "ti_attention_i8", "ti_tp_reduce_layernorm_q", "ti_tp_barrier", "ti_device_status",
+EXPORTS = ["ti_gemm_i8", "ti_gemm_workspace_bytes", "ti_gemm_i8_static_scratch", "ti_static_scratch_bytes", "ti_layernorm", "ti_gelu_q", "ti_softmax_q", "ti_attention_i8", "ti_tp_reduce_layernorm_q", "ti_gemm_i8_scatter", "ti_tp_barrier", "ti_device_status",
            "ti_version", "ti_last_error_string", "ti_launch_count", "ti_device_supported"]
 
 
@@ -71,13 +71,17 @@ class AttentionParams(C.Structure):
     ]
 
 
+class GemmScatter(C.Structure):
+    _fields_ = [("recv", C.c_void_p * 8), ("world", C.c_int32), ("rank", C.c_int32), ("rows_per_rank", C.c_int64)]
+
+
 class TpReduceLnParams(C.Structure):
     _fields_ = [
         ("parts", C.c_void_p * 8), ("outs", C.c_void_p * 8),
         ("residual_in", C.c_void_p), ("residual_out", C.c_void_p), ("bias_i32", C.c_void_p),
         ("gamma", C.c_void_p), ("beta", C.c_void_p), ("dq_scale_dev", C.c_void_p),
-        ("row_begin", C.c_int64), ("row_count", C.c_int64), ("n", C.c_int64),
-        ("eps", C.c_float), ("dq_scale", C.c_float), ("world", C.c_int32), ("rounding", C.c_int32),
+        ("row_begin", C.c_int64), ("row_count", C.c_int64), ("n", C.c_int64), ("parts_row_begin", C.c_int64),
+        ("eps", C.c_float), ("dq_scale", C.c_float), ("world", C.c_int32), ("rank", C.c_int32), ("rounding", C.c_int32),
         ("stream", C.c_void_p),
     ]
 
@@ -114,6 +118,8 @@ def load():
     lib.ti_attention_i8.restype = C.c_int
     lib.ti_tp_reduce_layernorm_q.argtypes = [C.POINTER(TpReduceLnParams)]
     lib.ti_tp_reduce_layernorm_q.restype = C.c_int
+    lib.ti_gemm_i8_scatter.argtypes = [C.POINTER(GemmParams), C.POINTER(GemmScatter)]
+    lib.ti_gemm_i8_scatter.restype = C.c_int
     lib.ti_tp_barrier.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_uint32, C.c_void_p]
     lib.ti_tp_barrier.restype = C.c_int
     lib.ti_device_status.argtypes = [C.POINTER(C.c_uint32)]

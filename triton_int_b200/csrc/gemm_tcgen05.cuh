@@ -43,6 +43,7 @@ struct Params {
   int bias_dtype, epilogue, rounding, causal;
   int c_vec_ok;  // c_stride_n == 1 and rows start on 16-byte boundaries
   int c_tma_ok;  // map_c is valid: output written with tensor stores
+  int rows_per_rank, rank;  // scatter mode: rows [r*rows_per_rank, ...) belong to rank r; this rank's slot index
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -340,10 +341,13 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const fl
   }
 }
 
+// `peer_maps` (scatter mode, else null): one output tensor map per tensor-parallel rank over
+// that rank's receive buffer [world][rows_per_rank][n]; a finished tile is stored straight
+// into the buffer of the rank that owns its rows (over NVLink for a peer), in the slot of
+// the storing rank, so the reduce-scatter traffic overlaps the remaining tiles' MMAs.
 template <int BN, int STAGES, typename OutT, int EPI>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                       const __grid_constant__ CUtensorMap map_c, const Params p) {
+__device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorMap* pb, const CUtensorMap* pc,
+                                          const CUtensorMap* peer_maps, const Params& p) {
   using S = Smem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -404,8 +408,8 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           const uint32_t a_dst = smem_base + stage * S::STAGE_BYTES;
           const uint32_t b_dst = a_dst + S::A_BYTES;
           mbar_expect_tx(full_bar(stage), S::STAGE_BYTES);
-          tma_load_3d(a_dst, &map_a, full_bar(stage), kb * BK, tile.m_blk * BM, tile.batch);
-          tma_load_3d(b_dst, &map_b, full_bar(stage), kb * BK, tile.n_blk * BN, tile.batch);
+          tma_load_3d(a_dst, pa, full_bar(stage), kb * BK, tile.m_blk * BM, tile.batch);
+          tma_load_3d(b_dst, pb, full_bar(stage), kb * BK, tile.n_blk * BN, tile.batch);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -545,7 +549,14 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             __syncwarp();
             if (lane == 0) {
               const int bcol = col0 + half * HALF_N + (chunk / CHUNKS_PER_BUF) * COLS_PER_BUF;
-              if (bcol < p.n && row0 < p.m) tma_store_3d(&map_c, buf_addr, bcol, row0, tile.batch);
+              if (bcol < p.n && row0 < p.m) {
+                if (peer_maps) {
+                  const int owner = row0 / p.rows_per_rank;
+                  tma_store_3d(peer_maps + owner, buf_addr, bcol, row0 - owner * p.rows_per_rank, p.rank);
+                } else {
+                  tma_store_3d(pc, buf_addr, bcol, row0, tile.batch);
+                }
+              }
               tma_store_commit();
             }
           }
@@ -588,6 +599,23 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+template <int BN, int STAGES, typename OutT, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const __grid_constant__ CUtensorMap map_c, const Params p) {
+  gemm_body<BN, STAGES, OutT, EPI>(&map_a, &map_b, &map_c, nullptr, p);
+}
+
+struct PeerMaps {
+  CUtensorMap m[8];
+};
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_i8_tcgen05_scatter_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                               const __grid_constant__ PeerMaps peers, const Params p) {
+  gemm_body<BN, STAGES, int32_t, TI_EPI_I32>(&map_a, &map_b, &peers.m[0], &peers.m[0], p);
 }
 
 // ------------------------------------------------------------------ host side
@@ -694,6 +722,7 @@ int launch_cfg(const ti_gemm_params& g, int num_sms) {
   p.epilogue = g.epilogue;
   p.rounding = g.rounding;
   p.causal = g.causal;
+  p.rows_per_rank = 0; p.rank = 0;
   const int64_t esz = (int64_t)sizeof(OutT);
   p.c_vec_ok = (g.c_stride_n == 1) && (((uintptr_t)g.c & 15) == 0) && ((g.c_stride_m * esz) % 16 == 0) &&
                ((g.c_stride_batch * esz) % 16 == 0);
@@ -718,6 +747,61 @@ int launch_cfg(const ti_gemm_params& g, int num_sms) {
   count_launch();
   TI_CUDA_CHECK(cudaGetLastError());
   return TI_OK;
+}
+
+// Row-parallel linear whose int32 tiles go straight to the ranks that own their rows.
+template <int BN, int STAGES>
+int launch_scatter_cfg(const ti_gemm_params& g, const ti_gemm_scatter& sc, int num_sms) {
+  using S = Smem<BN, STAGES>;
+  CUtensorMap map_a, map_b;
+  int rc = make_operand_map(&map_a, g.a, g.k, g.m, 1, g.a_stride_m, 0, BM);
+  if (rc != TI_OK) return rc;
+  rc = make_operand_map(&map_b, g.b, g.k, g.n, 1, g.b_stride_n, 0, BN);
+  if (rc != TI_OK) return rc;
+  PeerMaps peers;
+  memset(&peers, 0, sizeof(peers));
+  constexpr int ROW_BYTES = ((BN / 2) * 4 < 128) ? (BN / 2) * 4 : 128;
+  for (int r = 0; r < sc.world; ++r) {
+    rc = make_output_map(&peers.m[r], sc.recv[r], 4, g.n, sc.rows_per_rank, sc.world, g.n, sc.rows_per_rank * g.n,
+                         ROW_BYTES / 4, ROW_BYTES == 128);
+    if (rc != TI_OK) { set_error("scatter: tensor map over rank %d's receive buffer could not be encoded", r); return rc; }
+  }
+  Params p;
+  p.c = nullptr; p.bias = nullptr; p.alpha = nullptr; p.beta = nullptr;
+  p.c_stride_m = g.n; p.c_stride_n = 1; p.c_stride_batch = 0;
+  p.m = (int)g.m; p.n = (int)g.n; p.k = (int)g.k; p.batch = 1;
+  p.tiles_m = (int)((g.m + BM - 1) / BM);
+  p.tiles_n = (int)((g.n + BN - 1) / BN);
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.num_kb = (int)((g.k + BK - 1) / BK);
+  p.bias_dtype = TI_I32; p.epilogue = TI_EPI_I32; p.rounding = g.rounding; p.causal = 0;
+  p.c_vec_ok = 1; p.c_tma_ok = 1;
+  p.rows_per_rank = (int)sc.rows_per_rank; p.rank = sc.rank;
+  auto kern = gemm_i8_tcgen05_scatter_kernel<BN, STAGES>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    TI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::DYN_BYTES));
+    attr_set = true;
+  }
+  const int grid = p.num_tiles < num_sms ? p.num_tiles : num_sms;
+  kern<<<grid, NUM_THREADS, S::DYN_BYTES, (cudaStream_t)g.stream>>>(map_a, map_b, peers, p);
+  count_launch();
+  TI_CUDA_CHECK(cudaGetLastError());
+  return TI_OK;
+}
+
+inline int launch_scatter(const ti_gemm_params& g, const ti_gemm_scatter& sc, int num_sms) {
+  if (g.batch != 1 || !eligible(g)) { set_error("scatter: needs one K-contiguous, 16-byte aligned problem"); return TI_ERR_ALIGN; }
+  if (sc.world < 1 || sc.world > 8 || sc.rank < 0 || sc.rank >= sc.world) { set_error("scatter: bad world/rank"); return TI_ERR_UNSUPPORTED; }
+  if (sc.rows_per_rank <= 0 || sc.rows_per_rank % BM != 0 || sc.rows_per_rank * sc.world != g.m || (g.n % 4) != 0) {
+    set_error("scatter: rows_per_rank must be a multiple of 128 with world * rows_per_rank == m, and n a multiple of 4");
+    return TI_ERR_SHAPE;
+  }
+  for (int r = 0; r < sc.world; ++r)
+    if (!sc.recv[r] || ((uintptr_t)sc.recv[r] & 15)) { set_error("scatter: null or misaligned receive buffer %d", r); return TI_ERR_ALIGN; }
+  if (g.n > 128) return launch_scatter_cfg<256, 4>(g, sc, num_sms);
+  if (g.n > 64) return launch_scatter_cfg<128, 6>(g, sc, num_sms);
+  return launch_scatter_cfg<64, 8>(g, sc, num_sms);
 }
 
 template <typename OutT, int EPI>

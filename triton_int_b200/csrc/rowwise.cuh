@@ -313,7 +313,12 @@ __device__ __forceinline__ float consumer_sum(float v, float* red, int tid) {
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   if ((tid & 31) == 0) red[tid >> 5] = v;
   asm volatile("bar.sync 1, 256;" ::: "memory");
-  return ((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]));
+  // same left-to-right order over warps as row_reduce, so every LayerNorm kernel of this
+  // library produces the same statistics for the same row
+  float t = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) t += red[w];
+  return t;
 }
 
 template <bool DQ, int MAXV>

@@ -25,13 +25,13 @@ struct Params {
   const float* gamma;
   const float* beta;
   const float* dq_scale_dev;
-  int64_t row_begin, row_count, n;
+  int64_t row_begin, row_count, n, parts_row_begin;
   float eps, dq_scale;
-  int world, rounding;
+  int world, rank, rounding;
 };
 
 template <int MAXV>
-__global__ void __launch_bounds__(512, (MAXV <= 4 ? 2 : 1))
+__global__ void __launch_bounds__(512, 1)
 tp_reduce_layernorm_q_kernel(const Params p, const int tpr) {
   __shared__ float red[32 * 32];
   const int rows_per_cta = blockDim.x / tpr;
@@ -44,18 +44,38 @@ tp_reduce_layernorm_q_kernel(const Params p, const int tpr) {
   const float dq = p.dq_scale_dev ? *p.dq_scale_dev : p.dq_scale;
   float v[MAXV][4];
 
-  // all ranks' partial sums for this thread's columns are requested before any is used
+  // All ranks' partial sums for this thread's columns are requested before any is used.
+  // Rank q starts with rank q+1's buffer and ends with its own, so that at any moment
+  // the ranks pull from different sources instead of all draining the same GPU's links.
+  // Peers are visited four at a time: four peers' loads are in flight together.
   int4 acc[MAXV];
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) acc[i] = make_int4(0, 0, 0, 0);
-  for (int r = 0; r < p.world; ++r) {
-    const int32_t* src = p.parts[r] + grow * n;
 #pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
-      const int col = (i * tpr + tid) * 4;
-      if (row_ok && col < n) {
-        const int4 a = __ldcs(reinterpret_cast<const int4*>(src + col));
-        acc[i].x += a.x; acc[i].y += a.y; acc[i].z += a.z; acc[i].w += a.w;
+  for (int s0 = 0; s0 < MAX_WORLD; s0 += 4) {
+    if (s0 < p.world) {
+      int4 part[4][MAXV];
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        if (s0 + s < p.world) {
+          int r = p.rank + 1 + s0 + s;
+          if (r >= p.world) r -= p.world;
+          const int32_t* src = p.parts[r] + (p.parts_row_begin + lrow) * n;
+#pragma unroll
+          for (int i = 0; i < MAXV; ++i) {
+            const int col = (i * tpr + tid) * 4;
+            part[s][i] = (row_ok && col < n) ? __ldcs(reinterpret_cast<const int4*>(src + col)) : make_int4(0, 0, 0, 0);
+          }
+        }
+      }
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        if (s0 + s < p.world) {
+#pragma unroll
+          for (int i = 0; i < MAXV; ++i) {
+            acc[i].x += part[s][i].x; acc[i].y += part[s][i].y; acc[i].z += part[s][i].z; acc[i].w += part[s][i].w;
+          }
+        }
       }
     }
   }
@@ -109,7 +129,14 @@ tp_reduce_layernorm_q_kernel(const Params p, const int tpr) {
     char4 c;
     c.x = cast_i8(o[0], p.rounding); c.y = cast_i8(o[1], p.rounding);
     c.z = cast_i8(o[2], p.rounding); c.w = cast_i8(o[3], p.rounding);
-    for (int r = 0; r < p.world; ++r) *reinterpret_cast<char4*>(p.outs[r] + grow * n + col) = c;
+#pragma unroll
+    for (int s = 0; s < MAX_WORLD; ++s) {
+      if (s < p.world) {
+        int r = p.rank + 1 + s;
+        if (r >= p.world) r -= p.world;
+        *reinterpret_cast<char4*>(p.outs[r] + grow * n + col) = c;
+      }
+    }
   }
 }
 
@@ -164,7 +191,7 @@ inline int launch_barrier(uint32_t* const* pads, int world, int rank, uint32_t e
 }
 
 inline int launch(const ti_tp_reduce_ln_params& g) {
-  if (g.world < 1 || g.world > MAX_WORLD) { set_error("tp: world size must be 1..8"); return TI_ERR_UNSUPPORTED; }
+  if (g.world < 1 || g.world > MAX_WORLD || g.rank < 0 || g.rank >= g.world) { set_error("tp: world size must be 1..8 and rank inside it"); return TI_ERR_UNSUPPORTED; }
   if (g.row_count < 0 || g.n <= 0 || g.row_begin < 0) { set_error("tp: bad extents"); return TI_ERR_SHAPE; }
   if (g.row_count == 0) return TI_OK;
   if (g.n % 4 != 0) { set_error("tp: row length must be a multiple of 4"); return TI_ERR_ALIGN; }
@@ -185,9 +212,10 @@ inline int launch(const ti_tp_reduce_ln_params& g) {
   }
   p.residual_in = g.residual_in; p.residual_out = g.residual_out; p.bias_i32 = g.bias_i32;
   p.gamma = g.gamma; p.beta = g.beta; p.dq_scale_dev = g.dq_scale_dev;
-  p.row_begin = g.row_begin; p.row_count = g.row_count; p.n = g.n;
-  p.eps = g.eps; p.dq_scale = g.dq_scale; p.world = g.world; p.rounding = g.rounding;
+  p.row_begin = g.row_begin; p.row_count = g.row_count; p.n = g.n; p.parts_row_begin = g.parts_row_begin;
+  p.eps = g.eps; p.dq_scale = g.dq_scale; p.world = g.world; p.rank = g.rank; p.rounding = g.rounding;
   int maxv = 0;
+  // same thread layout as layernorm_vec_kernel, hence the same reduction order and the same bits
   const int tpr = row::pick_tpr(g.n, &maxv);
   if (maxv > 8) { set_error("tp: rows longer than 16384 are not supported"); return TI_ERR_UNSUPPORTED; }
   const int threads = tpr < 128 ? 128 : tpr;

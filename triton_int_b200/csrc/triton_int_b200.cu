@@ -264,6 +264,16 @@ int ti_tp_reduce_layernorm_q(const ti_tp_reduce_ln_params* p) {
   return ti::tp::launch(*p);
 }
 
+int ti_gemm_i8_scatter(const ti_gemm_params* g, const ti_gemm_scatter* sc) {
+  if (!g || !sc) { set_error("scatter: null params"); return TI_ERR_DEVICE; }
+  if (g->m <= 0 || g->n <= 0 || g->k <= 0) { set_error("scatter: empty problem"); return TI_ERR_SHAPE; }
+  DeviceInfo di;
+  int rc = require_device(&di);
+  if (rc != TI_OK) return rc;
+  if (!is_device_ptr(g->a) || !is_device_ptr(g->b)) { set_error("scatter: a and b must be device pointers"); return TI_ERR_DEVICE; }
+  return ti::tc::launch_scatter(*g, *sc, di.sms);
+}
+
 int ti_tp_barrier(uint32_t* const* pads, int32_t world, int32_t rank, uint32_t epoch, void* stream) {
   if (!pads) { set_error("tp barrier: null pads"); return TI_ERR_DEVICE; }
   DeviceInfo di;

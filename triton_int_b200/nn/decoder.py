@@ -150,3 +150,31 @@ class Int8DecoderBlock(torch.nn.Module):
         g8 = linear_a8_w8_bfp32_ofp32_GeLu_Q(h8, self.fc1_w, self.fc1_bias, self.fc1_alpha, self.fc1_mul)
         linear_a8_w8_b32_o32(g8, self.fc2_w, None, out=p0)
         return res2
+
+    @torch.no_grad()
+    def forward_tp_push(self, residual_shard, bufs, batch, seq, prev_bias=None):
+        """Tensor-parallel step in which the row-parallel GEMMs push their int32 tiles into
+        the owners' receive buffers while they run (``ti_gemm_i8_scatter``) and the owner adds
+        the slices locally inside the dequant+LayerNorm kernel, which also pushes its int8
+        rows to every rank.  ``bufs.partial[0]`` is used as this rank's receive buffer for the
+        fc2 slices (filled by the previous block), ``bufs.partial[1]`` for out_proj's.  Returns
+        the new residual shard; the fc2 slices of this block sit in the peers' buffers."""
+        from .. import tp
+        r0, rc = bufs.rank_rows()
+        p0_ptrs, p1_ptrs = bufs.partial[0][1], bufs.partial[1][1]
+        (x8, x8_ptrs), (h8, h8_ptrs) = bufs.act[0], bufs.act[1]
+        bufs.barrier()  # every rank's fc2 slices have landed in this rank's buffer 0
+        res1 = tp.reduce_layernorm_q(bufs.local_slots(0), x8_ptrs, (r0, rc), self.hidden, residual_shard, self.ln1_w,
+                                     self.ln1_b, self.eps, self.prev_scale, bias_int32=prev_bias, parts_row_begin=0,
+                                     rank=bufs.rank)
+        bufs.barrier()  # x8 is complete everywhere
+        attn = self.attention(x8, batch, seq)
+        tp.gemm_scatter(attn, self.out_w, p1_ptrs, bufs.rank, rc)
+        bufs.barrier()
+        res2 = tp.reduce_layernorm_q(bufs.local_slots(1), h8_ptrs, (r0, rc), self.hidden, res1, self.ln2_w, self.ln2_b,
+                                     self.eps, self.out_scale, bias_int32=self.out_bias, parts_row_begin=0,
+                                     rank=bufs.rank)
+        bufs.barrier()
+        g8 = linear_a8_w8_bfp32_ofp32_GeLu_Q(h8, self.fc1_w, self.fc1_bias, self.fc1_alpha, self.fc1_mul)
+        tp.gemm_scatter(g8, self.fc2_w, p0_ptrs, bufs.rank, rc)
+        return res2

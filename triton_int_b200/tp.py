@@ -19,7 +19,7 @@ from .kernels._gemm import scale_tensor
 
 
 def reduce_layernorm_q(parts_ptrs, outs_ptrs, rank_rows, n, residual_in, gamma, beta, eps, dq_scale,
-                       bias_int32=None, want_residual_out=True):
+                       bias_int32=None, want_residual_out=True, parts_row_begin=None, rank=None):
     """Launch the fused kernel for this rank's rows.
 
     parts_ptrs / outs_ptrs: device pointers (ints), one per rank, of the [rows, n]
@@ -54,14 +54,44 @@ def reduce_layernorm_q(parts_ptrs, outs_ptrs, rank_rows, n, residual_in, gamma, 
     else:
         p.dq_scale = float(dq_scale)
     p.row_begin, p.row_count, p.n = row_begin, row_count, n
+    p.parts_row_begin = row_begin if parts_row_begin is None else parts_row_begin
     p.eps = float(eps)
     p.world = world
+    p.rank = (row_begin // row_count if row_count else 0) if rank is None else rank
     p.rounding = config.rounding_mode()
     with torch.cuda.device(dev):
         p.stream = _lib.current_stream_ptr(dev)
         rc = _lib.load().ti_tp_reduce_layernorm_q(C.byref(p))
     _lib.check(rc, "ti_tp_reduce_layernorm_q")
     return res_out
+
+
+def gemm_scatter(a2d, w, recv_ptrs, rank, rows_per_rank):
+    """Row-parallel linear whose raw int32 tiles are stored, as they finish, into the receive
+    buffers of the ranks owning their rows (``ti_gemm_i8_scatter``).  a2d int8 [M, K_local],
+    w int8 [N, K_local]; recv_ptrs: one device pointer per rank to an int32 buffer laid out
+    [world][rows_per_rank][N] (rank r's tile rows land in slot ``rank`` of their owner)."""
+    _lib.require_cuda(a2d, w)
+    assert a2d.dim() == 2 and w.dim() == 2 and a2d.shape[1] == w.shape[1]
+    world = len(recv_ptrs)
+    p = _lib.GemmParams()
+    p.a, p.b = a2d.data_ptr(), w.data_ptr()
+    p.m, p.k = a2d.shape
+    p.n = w.shape[0]
+    p.batch = 1
+    p.a_stride_m, p.a_stride_k = a2d.stride(0), a2d.stride(1)
+    p.b_stride_n, p.b_stride_k = w.stride(0), w.stride(1)
+    p.out_dtype, p.epilogue = _lib.TI_I32, _lib.EPI_I32
+    p.rounding = config.rounding_mode()
+    sc = _lib.GemmScatter()
+    for r in range(world):
+        sc.recv[r] = recv_ptrs[r]
+    sc.world, sc.rank, sc.rows_per_rank = world, rank, rows_per_rank
+    dev = a2d.device
+    with torch.cuda.device(dev):
+        p.stream = _lib.current_stream_ptr(dev)
+        rc = _lib.load().ti_gemm_i8_scatter(C.byref(p), C.byref(sc))
+    _lib.check(rc, "ti_gemm_i8_scatter")
 
 
 class SymmetricBuffers:
@@ -98,6 +128,12 @@ class SymmetricBuffers:
     def rank_rows(self):
         per = self.rows // self.world
         return self.rank * per, per
+
+    def local_slots(self, i):
+        """Pointers to the `world` slices [rows/world, n] of this rank's receive buffer i."""
+        t, _ = self.partial[i]
+        step = (self.rows // self.world) * self.n * 4
+        return [t.data_ptr() + s * step for s in range(self.world)]
 
     def barrier(self):
         """All ranks' streams have reached this point before any proceeds (bounded wait on
