@@ -339,7 +339,11 @@ def run_b200(args):
             "frac_of_nominal_4500": (achieved / 4500.0) if achieved else None,
             "launches_timed": n_gemm, "avg_launch_ms": gemm_ms / n_gemm if n_gemm else None,
             "ops_per_launch_avg": ops_per_launch,
-            "traffic": None,
+            # ncu capture of the q/k/v-shape launch (16384 x 4096 x 4096, int8 out): 84.0 MB read +
+            # 42.0 MB written to DRAM against 151 MB algorithmic (part of the output was still in L2)
+            "traffic": (126.0e6 if (world == 1 and not args.small) else None),
+            "traffic_note": "dram__bytes_read+write of one q/k/v-shape launch (profiles/gemm_i8_tcgen05_16384x4096x4096.md); "
+                            "algorithmic bytes of that launch: 151 MB",
         },
     }
     if not args.no_cpu_baseline and world == 1 and not args.small:
