@@ -32,9 +32,25 @@ def test_linear_golden(golden, case):
 
 
 def test_bmm_golden(golden):
-    # K = 64 rows are 16-byte multiples: the NT operators take the tensor-map path
+    # K = 64 and N = 56... rows: the NT operators take the tensor-map path; the NN ("s8t_s8t")
+    # operand of the small case has 56-byte rows and stays on the stride-agnostic kernel
     with gemm_path("tcgen05"):
         run_bmm_golden(golden["bmm"], "small", nn_too=False)
+
+
+@pytest.mark.parametrize("B,M,N,K", [(3, 200, 256, 320), (2, 130, 48, 112), (1, 128, 384, 2048)])
+def test_bmm_nn_layout_on_tensor_cores(B, M, N, K):
+    """bmm_s8t_s8t_*: second operand [B, K, N] (N contiguous) read as an MN-major tile."""
+    g = synthetic.gen(33 + N)
+    a = synthetic.int8_normal((B, M, K), 30, g)
+    bt = synthetic.int8_normal((B, K, N), 30, g)
+    sc = torch.tensor(2e-3)
+    with gemm_path("tcgen05"):
+        acc = KB.bmm_s8t_s8t_s32t(dev(a), dev(bt))
+        y8 = KB.bmm_s8t_s8t_s8t(dev(a), dev(bt), dev(sc))
+    assert_status_clean()
+    assert_equal(acc, O.bmm_s8t_s8t_s32t(a, bt), "NN accumulators")
+    assert_equal(y8, O.bmm_s8t_s8t_s8t(a, bt, sc, O.RNE_SAT), "NN int8")
 
 
 def test_unaligned_is_refused_when_forced():

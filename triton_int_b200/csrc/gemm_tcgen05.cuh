@@ -43,6 +43,7 @@ struct Params {
   int bias_dtype, epilogue, rounding, causal;
   int c_vec_ok;  // c_stride_n == 1 and rows start on 16-byte boundaries
   int c_tma_ok;  // map_c is valid: output written with tensor stores
+  int b_mn_major;           // B is [K, N] with N contiguous ("s8t" second operand): MN-major smem tiles
   int rows_per_rank, rank;  // scatter mode: rows [r*rows_per_rank, ...) belong to rank r; this rank's slot index
 };
 
@@ -168,6 +169,18 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   d |= (uint64_t)(1024 >> 4) << 32;           // stride byte offset
   d |= (uint64_t)1 << 46;                     // version
   d |= (uint64_t)2 << 61;                     // SWIZZLE_128B
+  return d;
+}
+// MN-major, 128B-swizzled operand tile: rows are k, each row 128 contiguous bytes of n;
+// groups of 8 k-rows 1024 bytes apart (stride byte offset); the next 128-wide n chunk
+// `lbo_bytes` further (leading byte offset).
+__device__ __forceinline__ uint64_t make_smem_desc_mn_major(uint32_t saddr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(lbo_bytes >> 4) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
   return d;
 }
 // kind::i8 instruction descriptor: D = s32, A = B = signed int8, both K-major.
@@ -409,7 +422,14 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorM
           const uint32_t b_dst = a_dst + S::A_BYTES;
           mbar_expect_tx(full_bar(stage), S::STAGE_BYTES);
           tma_load_3d(a_dst, pa, full_bar(stage), kb * BK, tile.m_blk * BM, tile.batch);
-          tma_load_3d(b_dst, pb, full_bar(stage), kb * BK, tile.n_blk * BN, tile.batch);
+          if (p.b_mn_major) {
+            // [k rows][128 bytes of n] sub-tiles, one per 128 columns
+#pragma unroll
+            for (int c = 0; c < BN / 128; ++c)
+              tma_load_3d(b_dst + (uint32_t)(c * BK * 128), pb, full_bar(stage), tile.n_blk * BN + c * 128, kb * BK, tile.batch);
+          } else {
+            tma_load_3d(b_dst, pb, full_bar(stage), kb * BK, tile.n_blk * BN, tile.batch);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -445,12 +465,20 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorM
           const uint32_t a_src = smem_base + stage * S::STAGE_BYTES;
           const uint32_t b_src = a_src + S::A_BYTES;
           const uint64_t adesc = make_smem_desc(a_src);
-          const uint64_t bdesc = make_smem_desc(b_src);
+          if (p.b_mn_major) {
+            const uint64_t bdesc = make_smem_desc_mn_major(b_src, BK * 128);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            // advance 32 bytes of K inside the 128-byte swizzle row: +2 in 16-byte units
-            umma_i8(tmem_d, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                    (kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < BK / UMMA_K; ++k)  // 32 k-rows of 128 bytes per step: +4096 bytes
+              umma_i8(tmem_d, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(256 * k), idesc | (1u << 16),
+                      (kb > 0 || k > 0) ? 1u : 0u);
+          } else {
+            const uint64_t bdesc = make_smem_desc(b_src);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              // advance 32 bytes of K inside the 128-byte swizzle row: +2 in 16-byte units
+              umma_i8(tmem_d, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                      (kb > 0 || k > 0) ? 1u : 0u);
+            }
           }
           umma_commit(empty_bar(stage));  // the stage may be refilled once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -682,16 +710,40 @@ inline int make_output_map(CUtensorMap* map, void* base, int esz, int64_t n, int
 
 // True when the tensor-map path can address this problem: both operands K-contiguous,
 // 16-byte aligned bases and 16-byte multiple row/batch strides.
+// B given as [K, N] with N contiguous and not also K-contiguous.
+inline bool b_is_mn_major(const ti_gemm_params& g) { return g.b_stride_k != 1 && g.b_stride_n == 1; }
+
 inline bool eligible(const ti_gemm_params& g) {
   if (g.m <= 0 || g.n <= 0 || g.k <= 0 || g.batch <= 0) return false;
-  if (g.a_stride_k != 1 || g.b_stride_k != 1) return false;
+  if (g.a_stride_k != 1) return false;
   if (((uintptr_t)g.a & 15) || ((uintptr_t)g.b & 15)) return false;
-  if ((g.a_stride_m % 16) || (g.b_stride_n % 16)) return false;
-  if (g.a_stride_m < g.k || g.b_stride_n < g.k) return false;
+  if ((g.a_stride_m % 16) || g.a_stride_m < g.k) return false;
+  if (b_is_mn_major(g)) {
+    if ((g.b_stride_k % 16) || g.b_stride_k < g.n) return false;   // rows of K, 16-byte multiples
+  } else {
+    if (g.b_stride_k != 1 || (g.b_stride_n % 16) || g.b_stride_n < g.k) return false;
+  }
   if (g.batch > 1 && ((g.a_stride_batch % 16) || (g.b_stride_batch % 16))) return false;
   if (g.batch > 1 && (g.a_stride_batch <= 0 || g.b_stride_batch <= 0)) return false;
   if (g.m >= (1ll << 31) || g.n >= (1ll << 31) || g.k >= (1ll << 31) || g.batch >= (1ll << 31)) return false;
   return true;
+}
+
+// Tensor map over an MN-major B operand viewed as [batch][k][n] with n contiguous; box = 128 k-rows x 128 bytes of n.
+inline int make_operand_map_mn(CUtensorMap* map, const void* base, int64_t n, int64_t k, int64_t batch,
+                               int64_t k_stride, int64_t batch_stride) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return TI_ERR_CUDA; }
+  cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)k, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)k_stride, (cuuint64_t)(batch > 1 ? batch_stride : k_stride * k)};
+  if (strides[1] == 0 || (strides[1] % 16) != 0) strides[1] = 16;
+  cuuint32_t box[3] = {128, (cuuint32_t)BK, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (MN-major B) failed with CUresult %d", (int)r); return TI_ERR_CUDA; }
+  return TI_OK;
 }
 
 template <int BN, int STAGES, typename OutT, int EPI>
@@ -700,10 +752,13 @@ int launch_cfg(const ti_gemm_params& g, int num_sms) {
   CUtensorMap map_a, map_b;
   int rc = make_operand_map(&map_a, g.a, g.k, g.m, g.batch, g.a_stride_m, g.a_stride_batch, BM);
   if (rc != TI_OK) return rc;
-  rc = make_operand_map(&map_b, g.b, g.k, g.n, g.batch, g.b_stride_n, g.b_stride_batch, BN);
+  const bool mn = b_is_mn_major(g);
+  rc = mn ? make_operand_map_mn(&map_b, g.b, g.n, g.k, g.batch, g.b_stride_k, g.b_stride_batch)
+          : make_operand_map(&map_b, g.b, g.k, g.n, g.batch, g.b_stride_n, g.b_stride_batch, BN);
   if (rc != TI_OK) return rc;
 
   Params p;
+  p.b_mn_major = mn ? 1 : 0;
   p.c = g.c;
   p.bias = g.bias;
   p.alpha = g.alpha;
@@ -776,7 +831,7 @@ int launch_scatter_cfg(const ti_gemm_params& g, const ti_gemm_scatter& sc, int n
   p.num_kb = (int)((g.k + BK - 1) / BK);
   p.bias_dtype = TI_I32; p.epilogue = TI_EPI_I32; p.rounding = g.rounding; p.causal = 0;
   p.c_vec_ok = 1; p.c_tma_ok = 1;
-  p.rows_per_rank = (int)sc.rows_per_rank; p.rank = sc.rank;
+  p.rows_per_rank = (int)sc.rows_per_rank; p.rank = sc.rank; p.b_mn_major = 0;
   auto kern = gemm_i8_tcgen05_scatter_kernel<BN, STAGES>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -791,7 +846,7 @@ int launch_scatter_cfg(const ti_gemm_params& g, const ti_gemm_scatter& sc, int n
 }
 
 inline int launch_scatter(const ti_gemm_params& g, const ti_gemm_scatter& sc, int num_sms) {
-  if (g.batch != 1 || !eligible(g)) { set_error("scatter: needs one K-contiguous, 16-byte aligned problem"); return TI_ERR_ALIGN; }
+  if (g.batch != 1 || !eligible(g) || b_is_mn_major(g)) { set_error("scatter: needs one K-contiguous, 16-byte aligned problem"); return TI_ERR_ALIGN; }
   if (sc.world < 1 || sc.world > 8 || sc.rank < 0 || sc.rank >= sc.world) { set_error("scatter: bad world/rank"); return TI_ERR_UNSUPPORTED; }
   if (sc.rows_per_rank <= 0 || sc.rows_per_rank % BM != 0 || sc.rows_per_rank * sc.world != g.m || (g.n % 4) != 0) {
     set_error("scatter: rows_per_rank must be a multiple of 128 with world * rows_per_rank == m, and n a multiple of 4");
@@ -808,7 +863,7 @@ template <typename OutT, int EPI>
 int launch_epi(const ti_gemm_params& g, int num_sms) {
   // 128x256 tiles when N is wide enough to fill them, else 128x128 / 128x64
   if (g.n > 128) return launch_cfg<256, 4, OutT, EPI>(g, num_sms);
-  if (g.n > 64) return launch_cfg<128, 6, OutT, EPI>(g, num_sms);
+  if (g.n > 64 || b_is_mn_major(g)) return launch_cfg<128, 6, OutT, EPI>(g, num_sms);  // MN-major tiles are 128 columns wide
   return launch_cfg<64, 8, OutT, EPI>(g, num_sms);
 }
 
@@ -872,7 +927,7 @@ splitk_reduce_kernel(const ReduceParams p) {
 // than half of the SMs idle, K at least 8 stages long, N a multiple of 4.  The split count
 // divides the number of 128-byte K blocks so every part is whole.
 inline int pick_splits(const ti_gemm_params& g, int num_sms) {
-  if (g.batch != 1 || g.causal || (g.n % 4) != 0 || (g.k % BK) != 0) return 1;
+  if (g.batch != 1 || g.causal || (g.n % 4) != 0 || (g.k % BK) != 0 || b_is_mn_major(g)) return 1;
   const int bn = g.n > 128 ? 256 : (g.n > 64 ? 128 : 64);
   const int64_t tiles = ((g.m + BM - 1) / BM) * ((g.n + bn - 1) / bn);
   const int64_t kb = g.k / BK;
