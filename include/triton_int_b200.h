@@ -267,6 +267,38 @@ int ti_tp_barrier(uint32_t* const* pads, int32_t world, int32_t rank, uint32_t e
  * issuer, bit 2: epilogue).  Synchronises the device. */
 int ti_device_status(uint32_t* status_out);
 
+/*
+ * Dynamic activation quantisation on the GPU (absolute-maximum scaling), the step in front
+ * of a W8A8 linear when no static input scale exists:
+ *   per_token != 0: dynamic_quantize_activation_per_token_absmax  functional/quantization.py:54-61
+ *                   scales = [rows] in x's dtype
+ *   per_token == 0: dynamic_quantize_activation_per_tensor_absmax (clamp_min = 1, :46-51) or
+ *                   quantize_per_tensor_absmax (clamp_min = 0, :5-14); scales = float[2]:
+ *                   scales[0] receives the scale, scales[1] is working storage
+ * q = clamp(rint(x / scale), -128, 127) with the quotient rounded to x's dtype first, as
+ * torch's in-place div_().round_() does.  x is not modified (the reference helpers
+ * overwrite their argument).
+ */
+typedef struct {
+  const void* x;
+  int8_t* q;
+  void* scales;
+  int64_t rows, n;
+  int64_t x_row_stride, q_row_stride;   /* elements */
+  int32_t x_dtype;                      /* TI_F32 / TI_F16 / TI_BF16 */
+  int32_t per_token;
+  int32_t clamp_min;
+  void* stream;
+} ti_quantize_params;
+
+int ti_quantize_absmax(const ti_quantize_params* p);
+
+/* Test hook for the failure-reporting path: launches one thread that waits, with the
+ * library's bounded-wait loop, on a barrier nothing arrives at; after limit_us
+ * microseconds (1..100000) it sets bit 2 of the status word and returns.  The GPU is
+ * neither hung nor faulted and the context stays usable. */
+int ti_debug_expire_wait(uint32_t limit_us, void* stream);
+
 /* Library facts. */
 int ti_version(void);
 const char* ti_last_error_string(void);

@@ -115,3 +115,14 @@ def test_product_code_never_imports_the_oracle():
 def test_build_flags_target_sm100a_only():
     assert "arch=compute_100a,code=sm_100a" in _build.NVCC_FLAGS
     assert "-lineinfo" in _build.NVCC_FLAGS
+
+
+def test_reference_import_paths_resolve():
+    """Model code written against the reference's package name imports unchanged."""
+    from triton_int.functional.bmm import bmm_i8_o8  # noqa: F401
+    from triton_int.kernels.linear import linear_a8_w8_b8_o8  # noqa: F401
+    from triton_int.nn.bmm import BMM_S8T_S8N_F32T
+    from triton_int.nn.fused import DQ_Add_LayerNorm_Q, LayerNormQ  # noqa: F401
+    from triton_int.nn.linear import W8A8B8O8Linear, W8A8BFP32OFP32Linear  # noqa: F401
+    import triton_int_b200.nn.bmm as impl
+    assert BMM_S8T_S8N_F32T is impl.BMM_S8T_S8N_F32T

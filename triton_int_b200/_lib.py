@@ -23,7 +23,7 @@ PATH_AUTO, PATH_TCGEN05, PATH_GENERIC = range(3)
 DTYPE_CODE = {torch.int8: TI_I8, torch.int32: TI_I32, torch.float32: TI_F32,
               torch.float16: TI_F16, torch.bfloat16: TI_BF16}
 
-EXPORTS = ["ti_gemm_i8", "ti_gemm_workspace_bytes", "ti_gemm_i8_static_scratch", "ti_static_scratch_bytes", "ti_layernorm", "ti_gelu_q", "ti_softmax_q", "ti_attention_i8", "ti_tp_reduce_layernorm_q", "ti_gemm_i8_scatter", "ti_tp_barrier", "ti_device_status",
+EXPORTS = ["ti_gemm_i8", "ti_gemm_workspace_bytes", "ti_gemm_i8_static_scratch", "ti_static_scratch_bytes", "ti_layernorm", "ti_gelu_q", "ti_softmax_q", "ti_attention_i8", "ti_tp_reduce_layernorm_q", "ti_gemm_i8_scatter", "ti_tp_barrier", "ti_debug_expire_wait", "ti_quantize_absmax", "ti_device_status",
            "ti_version", "ti_last_error_string", "ti_launch_count", "ti_device_supported"]
 
 
@@ -69,6 +69,12 @@ class AttentionParams(C.Structure):
         ("p_mul", C.c_float), ("causal", C.c_int32), ("rounding", C.c_int32),
         ("stream", C.c_void_p),
     ]
+
+
+class QuantizeParams(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("q", C.c_void_p), ("scales", C.c_void_p),
+                ("rows", C.c_int64), ("n", C.c_int64), ("x_row_stride", C.c_int64), ("q_row_stride", C.c_int64),
+                ("x_dtype", C.c_int32), ("per_token", C.c_int32), ("clamp_min", C.c_int32), ("stream", C.c_void_p)]
 
 
 class GemmScatter(C.Structure):
@@ -122,6 +128,10 @@ def load():
     lib.ti_gemm_i8_scatter.restype = C.c_int
     lib.ti_tp_barrier.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_uint32, C.c_void_p]
     lib.ti_tp_barrier.restype = C.c_int
+    lib.ti_quantize_absmax.argtypes = [C.POINTER(QuantizeParams)]
+    lib.ti_quantize_absmax.restype = C.c_int
+    lib.ti_debug_expire_wait.argtypes = [C.c_uint32, C.c_void_p]
+    lib.ti_debug_expire_wait.restype = C.c_int
     lib.ti_device_status.argtypes = [C.POINTER(C.c_uint32)]
     lib.ti_device_status.restype = C.c_int
     lib.ti_version.restype = C.c_int

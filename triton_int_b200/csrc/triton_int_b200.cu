@@ -53,6 +53,7 @@ static int device_info(DeviceInfo* out) {
 #include "rowwise.cuh"
 #include "attention_tcgen05.cuh"
 #include "tp_fused.cuh"
+#include "quantize.cuh"
 
 using namespace ti;
 
@@ -188,6 +189,49 @@ int ti_gemm_i8_static_scratch(const ti_gemm_params* g) {
     local.workspace_bytes = TI_STATIC_SCRATCH_BYTES;
   }
   return ti_gemm_i8(&local);
+}
+
+// A kernel whose only job is to wait on a barrier that nothing ever arrives at, with the same
+// bounded-wait code path as the real kernels but a caller-chosen, short limit.  It lets a test
+// see the failure-reporting path (status word, context still usable) without hanging or
+// faulting the GPU.
+__global__ void ti_expire_wait_kernel(unsigned long long limit_ns) {
+  __shared__ unsigned long long bar;
+  const unsigned addr = (unsigned)__cvta_generic_to_shared(&bar);
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(addr) : "memory");
+  unsigned long long t0, t1;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (;;) {
+    if (ti::tc::mbar_try_wait(addr, 0)) return;  // cannot happen: nobody arrives
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (t1 - t0 > limit_ns) {
+      atomicOr(&ti::g_status, ti::STATUS_EPILOGUE);
+      return;
+    }
+  }
+}
+
+int ti_quantize_absmax(const ti_quantize_params* p) {
+  if (!p) { set_error("quantize: null params"); return TI_ERR_DEVICE; }
+  DeviceInfo di;
+  int rc = require_device(&di);
+  if (rc != TI_OK) return rc;
+  if (p->rows > 0 && (!is_device_ptr(p->x) || !is_device_ptr(p->q))) {
+    set_error("quantize: x and q must be device pointers (there is no CPU path)");
+    return TI_ERR_DEVICE;
+  }
+  return ti::quant::launch(*p, di.sms);
+}
+
+int ti_debug_expire_wait(uint32_t limit_us, void* stream) {
+  DeviceInfo di;
+  int rc = require_device(&di);
+  if (rc != TI_OK) return rc;
+  if (limit_us == 0 || limit_us > 100000) { set_error("debug wait: limit must be 1..100000 microseconds"); return TI_ERR_UNSUPPORTED; }
+  ti_expire_wait_kernel<<<1, 1, 0, (cudaStream_t)stream>>>((unsigned long long)limit_us * 1000ull);
+  count_launch();
+  TI_CUDA_CHECK(cudaGetLastError());
+  return TI_OK;
 }
 
 int64_t ti_gemm_workspace_bytes(const ti_gemm_params* g) {

@@ -74,3 +74,50 @@ def dequantize_activation_w_per_channel_a_per_token(q_act, w_scales, a_scales):
 def dequantize_activation_w_per_channel_a_per_tensor(q_act, w_scales, a_scales):
     out = q_act.to(torch.float32) * w_scales.reshape(1, -1) * a_scales
     return out.to(a_scales.dtype)
+
+
+# ---------------------------------------------------------------------------
+# Fused CUDA forms of the dynamic quantisers (one pass over the activations, input not
+# modified).  Same results as the helpers above on CUDA tensors.
+def _quantize_cuda(t, per_token, clamp_min):
+    import ctypes as C
+
+    from .. import _lib
+    _lib.require_cuda(t)
+    assert t.dtype in (torch.float32, torch.float16, torch.bfloat16)
+    n = t.shape[-1]
+    x2 = t.reshape(-1, n)
+    if x2.stride(1) != 1 or not per_token:
+        x2 = x2.contiguous()
+    q = torch.empty(t.shape, dtype=torch.int8, device=t.device)
+    p = _lib.QuantizeParams()
+    p.x, p.q = x2.data_ptr(), q.data_ptr()
+    p.rows, p.n = x2.shape
+    p.x_row_stride, p.q_row_stride = x2.stride(0) if x2.shape[0] > 1 else n, n
+    p.x_dtype = _lib.DTYPE_CODE[t.dtype]
+    p.per_token, p.clamp_min = (1 if per_token else 0), (1 if clamp_min else 0)
+    if per_token:
+        scales = torch.empty(t.shape[:-1] + (1,), dtype=t.dtype, device=t.device)
+    else:
+        scales = torch.empty(2, dtype=torch.float32, device=t.device)
+    p.scales = scales.data_ptr()
+    with torch.cuda.device(t.device):
+        p.stream = _lib.current_stream_ptr(t.device)
+        rc = _lib.load().ti_quantize_absmax(C.byref(p))
+    _lib.check(rc, "ti_quantize_absmax")
+    return q, (scales if per_token else scales[0].to(t.dtype))
+
+
+def dynamic_quantize_activation_per_token_absmax_cuda(t):
+    """(int8 tensor, [..., 1] scales): dynamic_quantize_activation_per_token_absmax in one kernel."""
+    return _quantize_cuda(t, True, True)
+
+
+def dynamic_quantize_activation_per_tensor_absmax_cuda(t):
+    """(int8 tensor, 0-dim scale): dynamic_quantize_activation_per_tensor_absmax in two kernels."""
+    return _quantize_cuda(t, False, True)
+
+
+def quantize_per_tensor_absmax_cuda(t):
+    """(int8 tensor, 0-dim scale): quantize_per_tensor_absmax without touching ``t``."""
+    return _quantize_cuda(t, False, False)

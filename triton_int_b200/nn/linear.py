@@ -138,8 +138,9 @@ class DynamicW8A8BFP32OFP32Linear(_W8A8Base):
         self.register_buffer("weight_scale", torch.tensor(alpha))
 
     def _op(self, x):
-        xq, scale = quantize_per_tensor_absmax(x.clone())
-        return linear_a8_w8_bfp32_ofp32(xq, self.weight, self.bias, scale * self.weight_scale, self.b)
+        from ..functional.quantization import quantize_per_tensor_absmax_cuda
+        xq, scale = quantize_per_tensor_absmax_cuda(x)   # fused absmax + quantise, x left untouched
+        return linear_a8_w8_bfp32_ofp32(xq, self.weight, self.bias, scale.float() * self.weight_scale, self.b)
 
     @classmethod
     def from_float(cls, module: torch.nn.Linear):
