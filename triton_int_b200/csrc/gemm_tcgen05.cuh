@@ -17,6 +17,7 @@
 #pragma once
 
 #include <cuda.h>
+#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 
@@ -43,6 +44,7 @@ struct Params {
   int bias_dtype, epilogue, rounding, causal;
   int c_vec_ok;  // c_stride_n == 1 and rows start on 16-byte boundaries
   int c_tma_ok;  // map_c is valid: output written with tensor stores
+  int debug_no_loads;       // timing experiment only: the producer signals stages full without loading
   int b_mn_major;           // B is [K, N] with N contiguous ("s8t" second operand): MN-major smem tiles
   int rows_per_rank, rank;  // scatter mode: rows [r*rows_per_rank, ...) belong to rank r; this rank's slot index
 };
@@ -116,6 +118,55 @@ __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bu
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// ---- CTA-pair (cta_group::2) forms: the two CTAs of a cluster compute one 256-row tile;
+// the even CTA issues the MMAs, each CTA loads its own A rows and its half of the B rows.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// tensor load whose completion is signalled on a barrier that may live in the peer CTA
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void umma_i8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
@@ -217,10 +268,10 @@ __device__ __forceinline__ bool tile_skipped(const Params& p, const Tile& t) {
 }
 
 // ------------------------------------------------------------------ shared memory
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool TWO_CTA = false>
 struct Smem {
   static constexpr int A_BYTES = BM * BK;
-  static constexpr int B_BYTES = BN * BK;
+  static constexpr int B_BYTES = (TWO_CTA ? BN / 2 : BN) * BK;   // a CTA pair splits the B tile
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
   // output staging: 8 epilogue warps x (32 rows x 128 bytes)
@@ -358,10 +409,16 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const fl
 // that rank's receive buffer [world][rows_per_rank][n]; a finished tile is stored straight
 // into the buffer of the rank that owns its rows (over NVLink for a peer), in the slot of
 // the storing rank, so the reduce-scatter traffic overlaps the remaining tiles' MMAs.
-template <int BN, int STAGES, typename OutT, int EPI>
+template <int BN, int STAGES, typename OutT, int EPI, bool TWO_CTA = false>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorMap* pb, const CUtensorMap* pc,
                                           const CUtensorMap* peer_maps, const Params& p) {
-  using S = Smem<BN, STAGES>;
+  using S = Smem<BN, STAGES, TWO_CTA>;
+  // CTA pair: rank 0 issues the MMAs for both; a work unit is a 256-row tile shared by the pair
+  const uint32_t pair_rank = TWO_CTA ? cluster_ctarank() : 0u;
+  const int unit = TWO_CTA ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int unit_stride = TWO_CTA ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  constexpr int TILE_M = TWO_CTA ? 2 * BM : BM;
+  constexpr int B_ROWS = TWO_CTA ? BN / 2 : BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
@@ -386,7 +443,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorM
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full_bar(b), 1);
-      mbar_init(acc_empty_bar(b), NUM_EPI_THREADS);
+      mbar_init(acc_empty_bar(b), TWO_CTA ? 2 * NUM_EPI_THREADS : NUM_EPI_THREADS);  // pair: both CTAs' epilogues
     }
     mbar_init(bias_ready_bar, NUM_EPI_THREADS);
     mbar_init(bias_free_bar, NUM_EPI_THREADS);
@@ -395,11 +452,17 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorM
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32((const void*)tmem_holder), TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (TWO_CTA) {
+      tmem_alloc_pair(smem_u32((const void*)tmem_holder), TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32((const void*)tmem_holder), TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (TWO_CTA) cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
@@ -409,7 +472,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorM
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < p.num_tiles && ok; t += unit_stride) {
         const Tile tile = decode_tile(t, p.tiles_m, p.tiles_n);
         if (tile_skipped<BN>(p, tile)) continue;
         for (int kb = 0; kb < p.num_kb; ++kb) {
@@ -420,6 +483,20 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorM
           }
           const uint32_t a_dst = smem_base + stage * S::STAGE_BYTES;
           const uint32_t b_dst = a_dst + S::A_BYTES;
+          if constexpr (TWO_CTA) {
+            // both CTAs' loads complete on the even CTA's barrier, which expects the pair's bytes
+            const uint32_t full_leader = map_to_cta(full_bar(stage), 0);
+            if (pair_rank == 0) mbar_expect_tx(full_bar(stage), 2 * S::STAGE_BYTES);
+            tma_load_3d_pair(a_dst, pa, full_leader, kb * BK, tile.m_blk * TILE_M + (int)pair_rank * BM, tile.batch);
+            tma_load_3d_pair(b_dst, pb, full_leader, kb * BK, tile.n_blk * BN + (int)pair_rank * B_ROWS, tile.batch);
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            continue;
+          }
+          if (p.debug_no_loads) {
+            mbar_arrive(full_bar(stage));
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           mbar_expect_tx(full_bar(stage), S::STAGE_BYTES);
           tma_load_3d(a_dst, pa, full_bar(stage), kb * BK, tile.m_blk * BM, tile.batch);
           if (p.b_mn_major) {
@@ -436,13 +513,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorM
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_i8(BM, BN);
+    if (lane == 0 && pair_rank == 0) {
+      constexpr uint32_t idesc = make_idesc_i8(TILE_M, BN);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < p.num_tiles && ok; t += unit_stride) {
         const Tile tile = decode_tile(t, p.tiles_m, p.tiles_n);
         if (tile_skipped<BN>(p, tile)) continue;
         const int buf = local & 1;
@@ -465,6 +542,17 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorM
           const uint32_t a_src = smem_base + stage * S::STAGE_BYTES;
           const uint32_t b_src = a_src + S::A_BYTES;
           const uint64_t adesc = make_smem_desc(a_src);
+          if constexpr (TWO_CTA) {
+            const uint64_t bdesc = make_smem_desc(b_src);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_i8_pair(tmem_d, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            // the stage is free in both CTAs once these MMAs have read it
+            umma_commit_pair(empty_bar(stage));
+            umma_commit_pair(map_to_cta(empty_bar(stage), 1));
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           if (p.b_mn_major) {
             const uint64_t bdesc = make_smem_desc_mn_major(b_src, BK * 128);
 #pragma unroll
@@ -483,7 +571,14 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorM
           umma_commit(empty_bar(stage));  // the stage may be refilled once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) umma_commit(acc_full_bar(buf));
+        if (ok) {
+          if constexpr (TWO_CTA) {
+            umma_commit_pair(acc_full_bar(buf));
+            umma_commit_pair(map_to_cta(acc_full_bar(buf), 1));
+          } else {
+            umma_commit(acc_full_bar(buf));
+          }
+        }
         ++local;
       }
     }
@@ -508,7 +603,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorM
     const bool has_bias = p.bias != nullptr;
     int local = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+    for (int t = unit; t < p.num_tiles && ok; t += unit_stride) {
       const Tile tile = decode_tile(t, p.tiles_m, p.tiles_n);
       if (tile_skipped<BN>(p, tile)) continue;
       const int buf = local & 1;
@@ -547,7 +642,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorM
         break;
       }
       tc_fence_after();
-      const int row0 = tile.m_blk * BM + quarter * 32;
+      const int row0 = tile.m_blk * TILE_M + (int)pair_rank * BM + quarter * 32;
       const int row = row0 + lane;
       const bool row_ok = row < p.m;
       OutT* c_row = reinterpret_cast<OutT*>(p.c) + (int64_t)tile.batch * p.c_stride_batch + (int64_t)row * p.c_stride_m;
@@ -596,7 +691,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorM
       auto release_acc = [&]() {
         // every accumulator this warp needs is in registers: hand the buffer back to the MMA warp
         tc_fence_before();
-        mbar_arrive(acc_empty_bar(buf));
+        if constexpr (TWO_CTA) mbar_arrive_cluster(map_to_cta(acc_empty_bar(buf), 0));  // the MMA issuer lives in the even CTA
+        else mbar_arrive(acc_empty_bar(buf));
       };
 
       // one call site for the chunk body keeps the instruction footprint small; the two
@@ -623,10 +719,21 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorM
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
     __syncthreads();
   }
+  if constexpr (TWO_CTA) cluster_sync_all();  // neither CTA frees TMEM or exits while its peer may still signal it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if constexpr (TWO_CTA) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+// CTA-pair variant: clusters of two CTAs, 256 x 256 output tile per pair (each CTA 128 rows),
+// K-major B only, six 32 KB stages per CTA.
+template <int STAGES, typename OutT, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                            const __grid_constant__ CUtensorMap map_c, const Params p) {
+  gemm_body<256, STAGES, OutT, EPI, true>(&map_a, &map_b, &map_c, nullptr, p);
 }
 
 template <int BN, int STAGES, typename OutT, int EPI>
@@ -759,6 +866,7 @@ int launch_cfg(const ti_gemm_params& g, int num_sms) {
 
   Params p;
   p.b_mn_major = mn ? 1 : 0;
+  { static const char* e = getenv("TI_DEBUG_NO_LOADS"); p.debug_no_loads = (e && e[0] == '1') ? 1 : 0; }
   p.c = g.c;
   p.bias = g.bias;
   p.alpha = g.alpha;
@@ -804,6 +912,72 @@ int launch_cfg(const ti_gemm_params& g, int num_sms) {
   return TI_OK;
 }
 
+// CTA-pair launch: 256 x 256 tiles, one per cluster of two CTAs.
+template <typename OutT, int EPI>
+int launch_pair_cfg(const ti_gemm_params& g, int num_sms) {
+  constexpr int STAGES = 6;
+  using S = Smem<256, STAGES, true>;
+  CUtensorMap map_a, map_b, map_c;
+  int rc = make_operand_map(&map_a, g.a, g.k, g.m, g.batch, g.a_stride_m, g.a_stride_batch, BM);
+  if (rc != TI_OK) return rc;
+  rc = make_operand_map(&map_b, g.b, g.k, g.n, g.batch, g.b_stride_n, g.b_stride_batch, 128);
+  if (rc != TI_OK) return rc;
+  Params p;
+  p.c = g.c; p.bias = g.bias; p.alpha = g.alpha; p.beta = g.beta;
+  p.c_stride_m = g.c_stride_m; p.c_stride_n = g.c_stride_n; p.c_stride_batch = g.c_stride_batch;
+  p.m = (int)g.m; p.n = (int)g.n; p.k = (int)g.k; p.batch = (int)g.batch;
+  p.tiles_m = (int)((g.m + 2 * BM - 1) / (2 * BM));
+  p.tiles_n = (int)((g.n + 255) / 256);
+  const int64_t nt = (int64_t)p.tiles_m * p.tiles_n * g.batch;
+  if (nt >= (1ll << 31)) { set_error("too many tiles"); return TI_ERR_SHAPE; }
+  p.num_tiles = (int)nt;
+  p.num_kb = (int)((g.k + BK - 1) / BK);
+  p.bias_dtype = g.bias_dtype; p.epilogue = g.epilogue; p.rounding = g.rounding; p.causal = 0;
+  p.b_mn_major = 0; p.debug_no_loads = 0; p.rows_per_rank = 0; p.rank = 0;
+  const int64_t esz = (int64_t)sizeof(OutT);
+  p.c_vec_ok = (g.c_stride_n == 1) && (((uintptr_t)g.c & 15) == 0) && ((g.c_stride_m * esz) % 16 == 0) &&
+               ((g.c_stride_batch * esz) % 16 == 0);
+  memset(&map_c, 0, sizeof(map_c));
+  p.c_tma_ok = 0;
+  if (p.c_vec_ok) {
+    constexpr int ROW_BYTES = (128 * (int)sizeof(OutT) < 128) ? 128 * (int)sizeof(OutT) : 128;
+    if (make_output_map(&map_c, g.c, (int)sizeof(OutT), g.n, g.m, g.batch, g.c_stride_m, g.c_stride_batch,
+                        ROW_BYTES / (int)sizeof(OutT), true) == TI_OK)
+      p.c_tma_ok = 1;
+  }
+  auto kern = gemm_i8_tcgen05_pair_kernel<STAGES, OutT, EPI>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    TI_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::DYN_BYTES));
+    attr_set = true;
+  }
+  const int pairs = num_sms / 2;
+  const int clusters = p.num_tiles < pairs ? p.num_tiles : pairs;
+  kern<<<2 * clusters, NUM_THREADS, S::DYN_BYTES, (cudaStream_t)g.stream>>>(map_a, map_b, map_c, p);
+  count_launch();
+  TI_CUDA_CHECK(cudaGetLastError());
+  return TI_OK;
+}
+
+// 0: never; 1: when the problem fills the pairs (default); 2: always when addressable
+inline int pair_mode() {
+  static int mode = -1;
+  if (mode < 0) {
+    const char* e = getenv("TRITON_INT_GEMM_PAIR");
+    mode = e ? atoi(e) : 1;
+  }
+  return mode;
+}
+inline bool use_pair(const ti_gemm_params& g, int num_sms) {
+  const int mode = pair_mode();
+  if (mode == 0 || b_is_mn_major(g) || g.causal || g.n <= 128 || g.m <= 128) return false;
+  // the GELU epilogue is the longer side of its tiles; waiting for two CTAs' epilogues costs more than the pair gains
+  if (mode == 1 && g.epilogue == TI_EPI_GELU_Q) return false;
+  if (mode == 2) return true;
+  const int64_t tiles = ((g.m + 255) / 256) * ((g.n + 255) / 256) * g.batch;
+  return tiles >= num_sms / 2 && g.k >= 1024;
+}
+
 // Row-parallel linear whose int32 tiles go straight to the ranks that own their rows.
 template <int BN, int STAGES>
 int launch_scatter_cfg(const ti_gemm_params& g, const ti_gemm_scatter& sc, int num_sms) {
@@ -831,7 +1005,7 @@ int launch_scatter_cfg(const ti_gemm_params& g, const ti_gemm_scatter& sc, int n
   p.num_kb = (int)((g.k + BK - 1) / BK);
   p.bias_dtype = TI_I32; p.epilogue = TI_EPI_I32; p.rounding = g.rounding; p.causal = 0;
   p.c_vec_ok = 1; p.c_tma_ok = 1;
-  p.rows_per_rank = (int)sc.rows_per_rank; p.rank = sc.rank; p.b_mn_major = 0;
+  p.rows_per_rank = (int)sc.rows_per_rank; p.rank = sc.rank; p.b_mn_major = 0; p.debug_no_loads = 0;
   auto kern = gemm_i8_tcgen05_scatter_kernel<BN, STAGES>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -861,6 +1035,7 @@ inline int launch_scatter(const ti_gemm_params& g, const ti_gemm_scatter& sc, in
 
 template <typename OutT, int EPI>
 int launch_epi(const ti_gemm_params& g, int num_sms) {
+  if (use_pair(g, num_sms)) return launch_pair_cfg<OutT, EPI>(g, num_sms);
   // 128x256 tiles when N is wide enough to fill them, else 128x128 / 128x64
   if (g.n > 128) return launch_cfg<256, 4, OutT, EPI>(g, num_sms);
   if (g.n > 64 || b_is_mn_major(g)) return launch_cfg<128, 6, OutT, EPI>(g, num_sms);  // MN-major tiles are 128 columns wide
