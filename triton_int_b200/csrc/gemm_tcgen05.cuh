@@ -44,7 +44,6 @@ struct Params {
   int bias_dtype, epilogue, rounding, causal;
   int c_vec_ok;  // c_stride_n == 1 and rows start on 16-byte boundaries
   int c_tma_ok;  // map_c is valid: output written with tensor stores
-  int debug_no_loads;       // timing experiment only: the producer signals stages full without loading
   int b_mn_major;           // B is [K, N] with N contiguous ("s8t" second operand): MN-major smem tiles
   int rows_per_rank, rank;  // scatter mode: rows [r*rows_per_rank, ...) belong to rank r; this rank's slot index
 };
@@ -492,11 +491,6 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorM
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             continue;
           }
-          if (p.debug_no_loads) {
-            mbar_arrive(full_bar(stage));
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-            continue;
-          }
           mbar_expect_tx(full_bar(stage), S::STAGE_BYTES);
           tma_load_3d(a_dst, pa, full_bar(stage), kb * BK, tile.m_blk * BM, tile.batch);
           if (p.b_mn_major) {
@@ -866,7 +860,6 @@ int launch_cfg(const ti_gemm_params& g, int num_sms) {
 
   Params p;
   p.b_mn_major = mn ? 1 : 0;
-  { static const char* e = getenv("TI_DEBUG_NO_LOADS"); p.debug_no_loads = (e && e[0] == '1') ? 1 : 0; }
   p.c = g.c;
   p.bias = g.bias;
   p.alpha = g.alpha;
@@ -933,7 +926,7 @@ int launch_pair_cfg(const ti_gemm_params& g, int num_sms) {
   p.num_tiles = (int)nt;
   p.num_kb = (int)((g.k + BK - 1) / BK);
   p.bias_dtype = g.bias_dtype; p.epilogue = g.epilogue; p.rounding = g.rounding; p.causal = 0;
-  p.b_mn_major = 0; p.debug_no_loads = 0; p.rows_per_rank = 0; p.rank = 0;
+  p.b_mn_major = 0; p.rows_per_rank = 0; p.rank = 0;
   const int64_t esz = (int64_t)sizeof(OutT);
   p.c_vec_ok = (g.c_stride_n == 1) && (((uintptr_t)g.c & 15) == 0) && ((g.c_stride_m * esz) % 16 == 0) &&
                ((g.c_stride_batch * esz) % 16 == 0);
@@ -1005,7 +998,7 @@ int launch_scatter_cfg(const ti_gemm_params& g, const ti_gemm_scatter& sc, int n
   p.num_kb = (int)((g.k + BK - 1) / BK);
   p.bias_dtype = TI_I32; p.epilogue = TI_EPI_I32; p.rounding = g.rounding; p.causal = 0;
   p.c_vec_ok = 1; p.c_tma_ok = 1;
-  p.rows_per_rank = (int)sc.rows_per_rank; p.rank = sc.rank; p.b_mn_major = 0; p.debug_no_loads = 0;
+  p.rows_per_rank = (int)sc.rows_per_rank; p.rank = sc.rank; p.b_mn_major = 0;
   auto kern = gemm_i8_tcgen05_scatter_kernel<BN, STAGES>;
   static bool attr_set = false;
   if (!attr_set) {

@@ -6,7 +6,7 @@
 // Each rank runs this kernel over its own slice of the rows; the fp32 residual
 // stream stays row-sharded.  There is no wait inside the kernel: ordering against
 // the producers of the partial sums and the consumers of the gathered rows is a
-// stream-level barrier supplied by the caller.  No TMA, no multicast.
+// stream-level barrier supplied by the caller.  Plain loads and stores only.
 #pragma once
 
 #include "rowwise.cuh"

@@ -5,8 +5,8 @@ One process per GPU.  ``torch.distributed`` (NCCL) is the control plane;
 the int32 partial sums and the gathered int8 activations live in symmetric
 memory (``torch.distributed._symmetric_memory``), which gives every rank a device
 pointer to every peer's buffer over NVLink.  The data path is this library's own
-kernel (``ti_tp_reduce_layernorm_q``): plain peer loads and stores, no TMA, no
-multicast.  Ordering between ranks is a device-side barrier on the current stream.
+kernel (``ti_tp_reduce_layernorm_q``): plain peer loads and stores only.
+Ordering between ranks is a device-side barrier on the current stream.
 """
 from __future__ import annotations
 
