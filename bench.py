@@ -42,10 +42,12 @@ def parse():
     ap.add_argument("--small", action="store_true", help="reduced shapes (profiling under ncu)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--tp-mode", default="fused", choices=["fused", "push", "nccl"],
+    ap.add_argument("--tp-mode", default="fused", choices=["fused", "dma", "push", "nccl"],
                     help="N>1: 'push' = row-parallel GEMMs store their tiles into the owners' buffers from the epilogue, "
                          "owner adds locally inside the LayerNorm kernel; 'fused' = LayerNorm kernel pulls the partial "
-                         "sums from every peer; 'nccl' = int32 all-reduce then LayerNorm")
+                         "sums from every peer; 'dma' = partial sums pushed to their owners by the copy engines "
+                         "(overlaps another group of sequences' kernels with --microbatches 2); "
+                         "'nccl' = int32 all-reduce then LayerNorm")
     ap.add_argument("--microbatches", type=int, default=1,
                     help="N>1, fused exchange: sequences are split into this many groups that run on their own "
                          "streams so one group's exchange overlaps the other's GEMMs")
@@ -203,7 +205,7 @@ def run_b200(args):
     tp_mode = "single" if world == 1 else args.tp_mode
     bufs = None
     nmb = 1
-    if tp_mode in ("fused", "push"):
+    if tp_mode in ("fused", "push", "dma"):
         # residual stream row-sharded; the int32 partial sums and the gathered int8
         # activations live in peer-mapped buffers, one set per group of sequences
         from triton_int_b200 import tp
@@ -216,7 +218,7 @@ def run_b200(args):
             if rank == 0:
                 print(f"[bench] symmetric memory unavailable ({exc}); using the NCCL all-reduce path", file=sys.stderr)
             tp_mode = "nccl"
-    if tp_mode in ("fused", "push"):
+    if tp_mode in ("fused", "push", "dma"):
         mb_tokens = tokens // nmb
         r0, rc = bufs[0].rank_rows()
         state = []
@@ -224,12 +226,15 @@ def run_b200(args):
             lo = i * mb_tokens
             state.append(residual[lo + r0:lo + r0 + rc].contiguous())
             bufs[i].partial[0][0].zero_()
-            if tp_mode == "push":
+            if tp_mode in ("push", "dma"):
                 # receive-buffer layout [world][rows/world][H]: the previous block's slices, all in slot 0
                 bufs[i].partial[0][0].view(world, rc, cfg["hidden"])[0].copy_(prev_acc[lo + r0:lo + r0 + rc])
             elif rank == 0:
                 bufs[i].partial[0][0].copy_(prev_acc[lo:lo + mb_tokens])   # the previous block's partial sums: all on rank 0 here
-        side = [torch.cuda.Stream(dev) for _ in range(nmb)]
+        # the first group's stream has priority, so the groups fall out of step and one group's
+        # copies run under the other's kernels instead of both copying at the same time
+        side = [torch.cuda.Stream(dev, priority=(-1 if (nmb > 1 and i == 0) else 0)) for i in range(nmb)]
+        comm = [torch.cuda.Stream(dev, priority=-1) for _ in range(nmb)]
         torch.cuda.synchronize()
         dist.barrier()
 
@@ -254,7 +259,7 @@ def run_b200(args):
     KF.gemm = timed_gemm
 
     def step():
-        if tp_mode in ("fused", "push"):
+        if tp_mode in ("fused", "push", "dma"):
             # chained like a stack of blocks: the fc2 partial sums left in the peer-mapped
             # buffer are the next step's input, the residual shard carries over.  Each group
             # of sequences runs on its own stream.
@@ -262,10 +267,15 @@ def run_b200(args):
             for i in range(nmb):
                 side[i].wait_stream(main)
                 with torch.cuda.stream(side[i]):
-                    fwd = block.forward_tp_push if tp_mode == "push" else block.forward_tp_fused
-                    state[i] = fwd(state[i], bufs[i], cfg["batch"] // nmb, cfg["seq"])
+                    if tp_mode == "dma":
+                        state[i] = block.forward_tp_dma(state[i], bufs[i], cfg["batch"] // nmb, cfg["seq"], comm[i])
+                    else:
+                        fwd = block.forward_tp_push if tp_mode == "push" else block.forward_tp_fused
+                        state[i] = fwd(state[i], bufs[i], cfg["batch"] // nmb, cfg["seq"])
             for i in range(nmb):
                 main.wait_stream(side[i])
+                if tp_mode == "dma":
+                    main.wait_stream(comm[i])
             return state
         return block(residual, prev_acc, cfg["batch"], cfg["seq"])
 

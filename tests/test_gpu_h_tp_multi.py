@@ -51,6 +51,18 @@ def _rank_main(rank, world, port, out):
     bufs2.barrier()
     mine = bufs2.partial[0][0].view(world, rc, h).sum(0, dtype=torch.int64).to(torch.int32)  # this rank's rows of fc2
     ok = ok and torch.equal(res_p, r_ref[r0:r0 + rc]) and torch.equal(mine, a_ref[r0:r0 + rc])
+    # the copy-engine form
+    bufs3 = tp.SymmetricBuffers(dist.group.WORLD, t, h, dev)
+    bufs3.partial[0][0].zero_()
+    bufs3.partial[0][0].view(world, rc, h)[0].copy_(p["prev_acc"].to(dev)[r0:r0 + rc])
+    torch.cuda.synchronize()
+    dist.barrier()
+    cs = torch.cuda.Stream(dev)
+    res_d = blk.forward_tp_dma(p["residual"].to(dev)[r0:r0 + rc].contiguous(), bufs3, 2, 128, cs)
+    torch.cuda.current_stream().wait_stream(cs)
+    bufs3.barrier()
+    mine_d = bufs3.partial[0][0].view(world, rc, h).sum(0, dtype=torch.int64).to(torch.int32)
+    ok = ok and torch.equal(res_d, r_ref[r0:r0 + rc]) and torch.equal(mine_d, a_ref[r0:r0 + rc])
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:

@@ -178,3 +178,41 @@ class Int8DecoderBlock(torch.nn.Module):
         g8 = linear_a8_w8_bfp32_ofp32_GeLu_Q(h8, self.fc1_w, self.fc1_bias, self.fc1_alpha, self.fc1_mul)
         tp.gemm_scatter(g8, self.fc2_w, p0_ptrs, bufs.rank, rc)
         return res2
+
+    @torch.no_grad()
+    def forward_tp_dma(self, residual_shard, bufs, batch, seq, comm_stream, prev_bias=None):
+        """Tensor-parallel step whose reduce-scatter traffic rides the copy engines: each
+        row-parallel GEMM writes a local [T, H] int32 matrix, its row slices are pushed to the
+        owners' receive buffers with asynchronous peer copies on ``comm_stream`` (no SM is
+        involved, so another group of sequences can compute meanwhile), and the owner adds the
+        slices locally inside the dequant+LayerNorm kernel.  Buffer roles as in forward_tp_push;
+        on return the pushes of this block's fc2 slices are in flight on ``comm_stream``."""
+        from .. import tp
+        r0, rc = bufs.rank_rows()
+        (x8, x8_ptrs), (h8, h8_ptrs) = bufs.act[0], bufs.act[1]
+        comp = torch.cuda.current_stream(residual_shard.device)
+        comp.wait_stream(comm_stream)   # the previous block's pushes from this rank are done
+        bufs.barrier()                  # ... and so are everybody else's
+        res1 = tp.reduce_layernorm_q(bufs.local_slots(0), x8_ptrs, (r0, rc), self.hidden, residual_shard, self.ln1_w,
+                                     self.ln1_b, self.eps, self.prev_scale, bias_int32=prev_bias, parts_row_begin=0,
+                                     rank=bufs.rank)
+        bufs.barrier()
+        attn = self.attention(x8, batch, seq)
+        part = bufs.staging(1)
+        linear_a8_w8_b32_o32(attn, self.out_w, None, out=part)
+        comm_stream.wait_stream(comp)
+        with torch.cuda.stream(comm_stream):
+            bufs.push_slices(1, part)
+        comp.wait_stream(comm_stream)
+        bufs.barrier()
+        res2 = tp.reduce_layernorm_q(bufs.local_slots(1), h8_ptrs, (r0, rc), self.hidden, res1, self.ln2_w, self.ln2_b,
+                                     self.eps, self.out_scale, bias_int32=self.out_bias, parts_row_begin=0,
+                                     rank=bufs.rank)
+        bufs.barrier()
+        g8 = linear_a8_w8_bfp32_ofp32_GeLu_Q(h8, self.fc1_w, self.fc1_bias, self.fc1_alpha, self.fc1_mul)
+        part2 = bufs.staging(0)
+        linear_a8_w8_b32_o32(g8, self.fc2_w, None, out=part2)
+        comm_stream.wait_stream(comp)
+        with torch.cuda.stream(comm_stream):
+            bufs.push_slices(0, part2)
+        return res2

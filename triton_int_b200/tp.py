@@ -104,12 +104,13 @@ class SymmetricBuffers:
         self.group, self.rows, self.n = group, rows, n
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         assert rows % self.world == 0, "rows must divide evenly over the ranks"
-        self.partial, self.act, self._handles = [], [], []
+        self.partial, self.act, self._handles, self._partial_handles = [], [], [], []
         for _ in range(num_partial):
             t = symm.empty((rows, n), dtype=torch.int32, device=device)
             h = symm.rendezvous(t, group)
             self.partial.append((t, [int(x) for x in h.buffer_ptrs]))
             self._handles.append(h)
+            self._partial_handles.append(h)
         for _ in range(num_act):
             t = symm.empty((rows, n), dtype=torch.int8, device=device)
             h = symm.rendezvous(t, group)
@@ -128,6 +129,30 @@ class SymmetricBuffers:
     def rank_rows(self):
         per = self.rows // self.world
         return self.rank * per, per
+
+    def staging(self, i):
+        """Local (not peer-mapped) [rows, n] int32 matrix a row-parallel GEMM writes before its row
+        slices are pushed to their owners; allocated on first use and kept."""
+        if not hasattr(self, "_staging"):
+            self._staging = {}
+        if i not in self._staging:
+            self._staging[i] = torch.empty((self.rows, self.n), dtype=torch.int32, device=self.partial[0][0].device)
+        return self._staging[i]
+
+    def peer_slot(self, i, peer):
+        """Tensor view [rows/world, n] of slot `self.rank` inside rank `peer`'s receive buffer i
+        (peer-mapped memory): the destination of this rank's copy-engine push to `peer`."""
+        per = self.rows // self.world
+        return self._partial_handles[i].get_buffer(peer, (per, self.n), torch.int32, self.rank * per * self.n)
+
+    def push_slices(self, i, partial):
+        """Copy rows [r*per, (r+1)*per) of this rank's [rows, n] int32 partial sums into slot
+        `rank` of rank r's receive buffer i, for every r, with asynchronous device-to-device
+        copies on the current stream (they run on the copy engines, not on SMs)."""
+        per = self.rows // self.world
+        for s in range(self.world):
+            r = (self.rank + 1 + s) % self.world   # staggered: every rank starts with a different peer
+            self.peer_slot(i, r).copy_(partial[r * per:(r + 1) * per], non_blocking=True)
 
     def local_slots(self, i):
         """Pointers to the `world` slices [rows/world, n] of this rank's receive buffer i."""
