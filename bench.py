@@ -317,7 +317,7 @@ def run_b200(args):
     # ---- end to end from host buffers: H2D inputs, block, D2H outputs, three streams
     e2e = None
     if not args.no_e2e:  # (host-buffer run uses the all-reduce form of the step at every N)
-        e2e = run_e2e(block, residual_h, acc_h, cfg, dev, world, dist, max(3, args.steps // 2), barrier)
+        e2e = run_e2e(block, residual_h, acc_h, cfg, dev, world, dist, max(3, args.steps), barrier)
 
     if rank != 0:
         if world > 1:
@@ -368,41 +368,50 @@ def run_b200(args):
 
 def run_e2e(block, residual_h, acc_h, cfg, dev, world, dist, steps, barrier):
     """Same block, inputs in pinned host memory: every step copies both inputs to the
-    device, runs the block and copies both outputs back.  Copies run on their own
-    streams with double buffering so step i+1's upload and step i-1's download
-    overlap step i's kernels."""
+    device, runs the block and copies both outputs back.  A step moves as groups of
+    sequences (sequences are independent of one another in a decoder block): uploads,
+    kernels and downloads run on three streams over a ring of group-sized buffers, so
+    one group's upload and another's download overlap a third's kernels, and the
+    pipeline's fill and drain cost one group, not one step."""
     tokens = cfg["batch"] * cfg["seq"]
+    groups = 4 if cfg["batch"] % 4 == 0 else (2 if cfg["batch"] % 2 == 0 else 1)
+    gb = cfg["batch"] // groups          # sequences per group
+    gt = gb * cfg["seq"]                 # tokens per group
+    ring = 3
     h2d, d2h = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     comp = torch.cuda.current_stream(dev)
-    din = [(torch.empty_like(residual_h, device=dev), torch.empty_like(acc_h, device=dev)) for _ in range(2)]
-    hout = [(torch.empty_like(residual_h).pin_memory(), torch.empty_like(acc_h).pin_memory()) for _ in range(2)]
-    up_done = [torch.cuda.Event() for _ in range(2)]
-    in_free = [torch.cuda.Event() for _ in range(2)]
-    out_ready = [torch.cuda.Event() for _ in range(2)]
-    out_free = [torch.cuda.Event() for _ in range(2)]
-    dout = [None, None]
+    hid = residual_h.shape[-1]
+    din = [(torch.empty((gt, hid), dtype=residual_h.dtype, device=dev),
+            torch.empty((gt, hid), dtype=acc_h.dtype, device=dev)) for _ in range(ring)]
+    hout = [(torch.empty((gt, hid), dtype=residual_h.dtype).pin_memory(),
+             torch.empty((gt, hid), dtype=acc_h.dtype).pin_memory()) for _ in range(ring)]
+    up_done = [torch.cuda.Event() for _ in range(ring)]
+    in_free = [torch.cuda.Event() for _ in range(ring)]
+    out_ready = [torch.cuda.Event() for _ in range(ring)]
+    out_free = [torch.cuda.Event() for _ in range(ring)]
 
-    def upload(i):
-        b = i & 1
+    def upload(j):
+        b, g = j % ring, j % groups
         with torch.cuda.stream(h2d):
             h2d.wait_event(in_free[b])
-            din[b][0].copy_(residual_h, non_blocking=True)
-            din[b][1].copy_(acc_h, non_blocking=True)
+            din[b][0].copy_(residual_h[g * gt:(g + 1) * gt], non_blocking=True)
+            din[b][1].copy_(acc_h[g * gt:(g + 1) * gt], non_blocking=True)
             up_done[b].record(h2d)
 
     def run(n):
-        for b in range(2):
+        total = n * groups
+        for b in range(ring):
             in_free[b].record(comp)
             out_free[b].record(d2h)
-        upload(0)
-        for i in range(n):
-            b = i & 1
-            if i + 1 < n:
-                upload(i + 1)
+        for j in range(min(ring - 1, total)):
+            upload(j)
+        for j in range(total):
+            b = j % ring
+            if j + ring - 1 < total:
+                upload(j + ring - 1)
             comp.wait_event(up_done[b])
             comp.wait_event(out_free[b])
-            r, a = block(din[b][0], din[b][1], cfg["batch"], cfg["seq"])
-            dout[b] = (r, a)
+            r, a = block(din[b][0], din[b][1], gb, cfg["seq"])
             in_free[b].record(comp)
             out_ready[b].record(comp)
             with torch.cuda.stream(d2h):
@@ -429,7 +438,8 @@ def run_e2e(block, residual_h, acc_h, cfg, dev, world, dist, steps, barrier):
     nbytes = residual_h.numel() * 4 + acc_h.numel() * 4
     return {"value": tokens / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "steps": steps,
             "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
-            "note": "pinned host buffers; upload, kernels and download pipelined on three streams"}
+            "note": "pinned host buffers; upload, kernels and download pipelined on three streams in %d groups "
+                    "of %d sequences per step" % (groups, gb)}
 
 
 def main():
