@@ -316,6 +316,37 @@ __device__ __forceinline__ uint32_t pack4_low_bytes(uint32_t a, uint32_t b, uint
   return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
 
+// Packed fp32 pairs with explicit rounding in the instruction, so that a multiply and the
+// add that follows it are never contracted into one fused multiply-add (the epilogues
+// round after every operation, as the reference's element-wise arithmetic does).
+__device__ __forceinline__ float2 mul2_rn(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 add2_rn(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 fma2_rn(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+
 // GELU-quant value before the int8 cast: gelu_tanh(x) * scale with
 // 0.5*x*(1+tanh(u)) rewritten as x - x / (exp(2u) + 1) (two special-function
 // operations per element).  Differs from the operation-by-operation form of
@@ -350,25 +381,49 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const fl
 #pragma unroll
     for (int j = 0; j < 32; ++j) f[j] = __fmul_rn(__int2float_rn((int32_t)r[j]), alpha);
   } else if constexpr (epilogue == TI_EPI_GELU_Q) {
+    // gelu_q_fast on two elements at a time with the packed fp32 instructions: every
+    // operation rounds as its scalar form does, so the results are those of gelu_q_fast
+    const float2 a2 = make_float2(alpha, alpha), s2 = make_float2(beta, beta);
+    const float2 c2 = make_float2(2.302208198f, 2.302208198f), c2k = make_float2(0.1029432397f, 0.1029432397f);
+    const float2 neg1 = make_float2(-1.0f, -1.0f);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const float x = __fadd_rn(__fmul_rn(__int2float_rn((int32_t)r[j]), alpha), bias_c ? bias_c[j] : 0.f);
-      f[j] = gelu_q_fast(x, beta);
+    for (int j = 0; j < 32; j += 2) {
+      float2 x = mul2_rn(make_float2(__int2float_rn((int32_t)r[j]), __int2float_rn((int32_t)r[j + 1])), a2);
+      x = add2_rn(x, bias_c ? *reinterpret_cast<const float2*>(bias_c + j) : make_float2(0.f, 0.f));
+      const float2 u = mul2_rn(x, fma2_rn(mul2_rn(x, x), c2k, c2));
+      float e0, e1, r0, r1;
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(u.x));
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(u.y));
+      const float2 d = fma2_rn(make_float2(e0, e1), neg1, neg1);   // -(e + 1): its reciprocal is -1/(e + 1)
+      asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(d.x));
+      asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(d.y));
+      const float2 g = mul2_rn(fma2_rn(x, make_float2(r0, r1), x), s2);
+      f[j] = g.x;
+      f[j + 1] = g.y;
     }
   } else {  // scale + bias (+ ReLU)
+    const float2 a2 = make_float2(alpha, alpha);
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      f[j] = __fadd_rn(bias_c ? bias_c[j] : 0.f, __fmul_rn(__int2float_rn((int32_t)r[j]), alpha));
+    for (int j = 0; j < 32; j += 2) {
+      const float2 x = mul2_rn(make_float2(__int2float_rn((int32_t)r[j]), __int2float_rn((int32_t)r[j + 1])), a2);
+      const float2 y = add2_rn(bias_c ? *reinterpret_cast<const float2*>(bias_c + j) : make_float2(0.f, 0.f), x);
+      f[j] = y.x;
+      f[j + 1] = y.y;
+    }
   }
   if constexpr (std::is_same<OutT, int8_t>::value) {
     constexpr bool relu = (epilogue == TI_EPI_SCALE_BIAS_RELU);
     if (rounding == TI_ROUND_RNE_SAT) {
+      const float2 magic2 = make_float2(12582912.0f, 12582912.0f);
+      const float lo = relu ? 0.f : -128.0f;   // ReLU folded into the lower clamp
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
-        uint32_t b[4];
+        float c[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) b[i] = quant_rne_sat_bits(relu ? fmaxf(f[j + i], 0.f) : f[j + i]);
-        vw[j >> 2] = pack4_low_bytes(b[0], b[1], b[2], b[3]);
+        for (int i = 0; i < 4; ++i) c[i] = fminf(fmaxf(f[j + i], lo), 127.0f);
+        const float2 b01 = add2_rn(make_float2(c[0], c[1]), magic2);   // round half even; low byte = int8
+        const float2 b23 = add2_rn(make_float2(c[2], c[3]), magic2);
+        vw[j >> 2] = pack4_low_bytes(__float_as_uint(b01.x), __float_as_uint(b01.y), __float_as_uint(b23.x), __float_as_uint(b23.y));
       }
     } else {
 #pragma unroll
