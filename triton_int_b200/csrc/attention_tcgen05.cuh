@@ -32,6 +32,7 @@ constexpr int KS = 4;                  // K ring stages
 constexpr int VS = 3;                  // V ring stages
 constexpr int ATT_THREADS = 576;
 constexpr int GROUP_THREADS = 256;  // one softmax group: 128 rows x 2 column halves
+constexpr int GROUP_WARPS = GROUP_THREADS / 32;  // barriers signalled by a group count one arrival per warp
 constexpr uint32_t MAGIC_BITS = 0x4B400000u;  // bits of 12582912.0f = 1.5 * 2^23
 constexpr float MAGIC_F = 12582912.0f;
 
@@ -148,11 +149,11 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     for (int i = 0; i < KS; ++i) { mbar_init(k_full0 + 8 * i, 1); mbar_init(k_empty0 + 8 * i, 1); }
     for (int i = 0; i < VS; ++i) { mbar_init(v_full0 + 8 * i, 1); mbar_init(v_empty0 + 8 * i, 1); }
     for (int g = 0; g < 2; ++g) {
-      mbar_init(s_full0 + 8 * g, 1); mbar_init(s_empty0 + 8 * g, GROUP_THREADS);
-      mbar_init(p_full0 + 8 * g, GROUP_THREADS); mbar_init(p_empty0 + 8 * g, 1);
+      mbar_init(s_full0 + 8 * g, 1); mbar_init(s_empty0 + 8 * g, GROUP_WARPS);
+      mbar_init(p_full0 + 8 * g, GROUP_WARPS); mbar_init(p_empty0 + 8 * g, 1);
     }
-    mbar_init(o_full, 1); mbar_init(o_empty, 2 * GROUP_THREADS);
-    mbar_init(stat_bar, 2 * GROUP_THREADS); mbar_init(stg_free, 2 * GROUP_THREADS); mbar_init(stg_full, 2 * GROUP_THREADS);
+    mbar_init(o_full, 1); mbar_init(o_empty, 2 * GROUP_WARPS);
+    mbar_init(stat_bar, 2 * GROUP_WARPS); mbar_init(stg_free, 2 * GROUP_WARPS); mbar_init(stg_full, 2 * GROUP_WARPS);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -284,13 +285,13 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       uint32_t acc[2][32];
 
       auto load_scores = [&]() -> bool {
-        if (!mbar_wait(s_full0 + 8 * g, s_cnt & 1u, abort_flag)) return false;
+        if (!mbar_wait_warp(s_full0 + 8 * g, s_cnt & 1u, abort_flag)) return false;
         tc_fence_after();
         const uint32_t ta = tmem_s0 + lane_addr + (uint32_t)(g * BKV + half * 64);
         tmem_ld32(ta, acc[0]); tmem_ld32(ta + 32, acc[1]);
         tmem_ld_wait();
         tc_fence_before();
-        mbar_arrive(s_empty0 + 8 * g);
+        mbar_arrive_warp(s_empty0 + 8 * g);
         ++s_cnt;
         return true;
       };
@@ -347,8 +348,8 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // ---- combine the four partial statistics of the row (2 groups x 2 halves)
       stat_m[slot] = m_run;
       stat_l[slot] = l_run;
-      mbar_arrive(stat_bar);
-      if (!mbar_wait(stat_bar, item_par, abort_flag)) { ok = false; break; }
+      mbar_arrive_warp(stat_bar);
+      if (!mbar_wait_warp(stat_bar, item_par, abort_flag)) { ok = false; break; }
       {
         int m = INT_LOW;
 #pragma unroll
@@ -370,7 +371,7 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // ---- pass 2: quantised probabilities into shared memory
       for (int j = g; j < n; j += 2) {
         if (!load_scores()) { ok = false; break; }
-        if (!mbar_wait(p_empty0 + 8 * g, (p_cnt & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(p_empty0 + 8 * g, (p_cnt & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         const int nvalid = limit - j * BKV - half * 64;
         const uint32_t prow = sb + S::P_OFF + (uint32_t)(g * TILE_BYTES + r * 128);
         const float2 lgn2 = make_float2(lgn, lgn);
@@ -405,23 +406,23 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           }
         }
         fence_async_smem();
-        mbar_arrive(p_full0 + 8 * g);
+        mbar_arrive_warp(p_full0 + 8 * g);
         ++p_cnt;
       }
       if (!ok) break;
 
       // ---- epilogue: O (int32 in TMEM) -> int8, 32 of the 128 head-dimension columns per thread
-      if (!mbar_wait(o_full, item_par, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(o_full, item_par, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int oq = g * 2 + half;  // which 32 columns
       uint32_t o32[32];
       tmem_ld32(tmem_o + lane_addr + (uint32_t)(oq * 32), o32);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(o_empty);
+      mbar_arrive_warp(o_empty);
       if (threadIdx.x == 64) tma_store_wait_read<0>();  // the previous item's store has left the staging tile
-      mbar_arrive(stg_free);
-      if (!mbar_wait(stg_free, item_par, abort_flag)) { ok = false; break; }
+      mbar_arrive_warp(stg_free);
+      if (!mbar_wait_warp(stg_free, item_par, abort_flag)) { ok = false; break; }
       {
         const uint32_t orow = sb + S::O_OFF + (uint32_t)(r * 128);
 #pragma unroll
@@ -443,11 +444,13 @@ attention_i8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
       }
       fence_async_smem();
-      mbar_arrive(stg_full);
-      if (threadIdx.x == 64) {
-        if (!mbar_wait(stg_full, item_par, abort_flag)) { ok = false; break; }
-        tma_store_4d(&map_o, sb + S::O_OFF, 0, it.h, it.qi * BQ, it.b);
-        tma_store_commit();
+      mbar_arrive_warp(stg_full);
+      if (warp == 2) {  // the warp whose first lane owns the output stores
+        if (!mbar_wait_warp(stg_full, item_par, abort_flag)) { ok = false; break; }
+        if (lane == 0) {
+          tma_store_4d(&map_o, sb + S::O_OFF, 0, it.h, it.qi * BQ, it.b);
+          tma_store_commit();
+        }
       }
     }
     if (!ok && lane == 0) atomicOr(&g_status, STATUS_EPILOGUE);

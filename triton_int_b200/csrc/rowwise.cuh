@@ -336,7 +336,7 @@ layernorm_stream_kernel(const LnParams p, const int stages) {
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(full0 + 8 * s), "r"(1) : "memory");
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty0 + 8 * s), "r"(CONSUMERS) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty0 + 8 * s), "r"(CONSUMERS / 32) : "memory");  // one arrival per consumer warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -410,8 +410,10 @@ layernorm_stream_kernel(const LnParams p, const int stages) {
         }
       }
     }
-    // the row is in registers: hand the slot back to the producer
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8 * s) : "memory");
+    // the row is in registers: hand the slot back to the producer (the warp meets first, so
+    // every lane's reads are ordered before the one arrival)
+    __syncwarp();
+    if ((tid & 31) == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8 * s) : "memory");
     if (++s == stages) { s = 0; ph ^= 1u; }
     if (DQ && p.residual_out) {
 #pragma unroll
