@@ -1055,8 +1055,6 @@ inline int pair_mode() {
 inline bool use_pair(const ti_gemm_params& g, int num_sms) {
   const int mode = pair_mode();
   if (mode == 0 || b_is_mn_major(g) || g.causal || g.n <= 128 || g.m <= 128) return false;
-  // the GELU epilogue is the longer side of its tiles; waiting for two CTAs' epilogues costs more than the pair gains
-  if (mode == 1 && g.epilogue == TI_EPI_GELU_Q) return false;
   if (mode == 2) return true;
   const int64_t tiles = ((g.m + 255) / 256) * ((g.n + 255) / 256) * g.batch;
   return tiles >= num_sms / 2 && g.k >= 1024;
