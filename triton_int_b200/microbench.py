@@ -3,8 +3,8 @@
     python -m triton_int_b200.microbench --op linear|lnq|gelu|attention|sweep [--iters N] [--rows R] ...
 
 Every line printed is one JSON object: the operator, its shape, the median CUDA-event
-time over `--iters` launches (L2 flushed before each launch for the memory-bound
-operators), the algorithmic work, the achieved rate and its fraction of the
+time over `--iters` launches (L2 flushed before each launch; problems of M <= 1024
+are timed as CUDA-graph replays), the algorithmic work, the achieved rate and its fraction of the
 measured peak (MEASURED_PEAKS.json next to the package's parent, else the
 fallback 6650 GB/s / 2 x 1400 TOP/s).
 """
@@ -111,10 +111,12 @@ def bench_linear(m, n, k, iters, epilogues=("i32", "b8o8", "f32", "geluq"), cubl
             emit(f"linear_{name}", [m, n, k], timeit_graph(fns[name], iters), ops=2 * m * n * k,
                  nbytes=m * k + n * k + out_bytes, timing="cuda graph replay (device time per call)")
         else:
-            emit(f"linear_{name}", [m, n, k], timeit(fns[name], iters), ops=2 * m * n * k)
+            # flushed: operands of the mid-size problems fit the L2, and the flush kernel keeps the GPU
+            # busy while the host prepares the launch (an idle GPU would count the host's time)
+            emit(f"linear_{name}", [m, n, k], timeit(fns[name], iters, flush=True), ops=2 * m * n * k)
     if cublas and m > 16 and m % 8 == 0 and n % 8 == 0 and k % 8 == 0:
         emit("cublaslt_int_mm (torch._int_mm, for comparison)", [m, n, k],
-             timeit(lambda: torch._int_mm(x, w.t()), iters), ops=2 * m * n * k)
+             timeit(lambda: torch._int_mm(x, w.t()), iters, flush=True), ops=2 * m * n * k)
 
 
 def bench_lnq(rows, hidden, iters):
