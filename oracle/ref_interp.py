@@ -28,9 +28,14 @@ import sys
 _REF = None
 
 
+def reference_root():
+    """Directory of the reference checkout, named by the TRITON_INT_REFERENCE environment variable."""
+    return os.environ.get("TRITON_INT_REFERENCE", "")
+
+
 def available() -> bool:
-    root = os.environ.get("TRITON_INT_REFERENCE", "/root/reference")
-    return os.path.isdir(os.path.join(root, "triton_int", "kernels"))
+    root = reference_root()
+    return bool(root) and os.path.isdir(os.path.join(root, "triton_int", "kernels"))
 
 
 def load():
@@ -43,7 +48,7 @@ def load():
     if "triton" in sys.modules and os.environ.get("TRITON_INTERPRET") != "1":
         raise RuntimeError("triton was imported before TRITON_INTERPRET=1 was set")
     os.environ["TRITON_INTERPRET"] = "1"
-    root = os.environ.get("TRITON_INT_REFERENCE", "/root/reference")
+    root = reference_root()
     if root not in sys.path:
         sys.path.insert(0, root)
 
