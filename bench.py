@@ -342,7 +342,7 @@ def run_b200(args):
         "e2e": e2e,
         "gpu_launches": int(launches),
         "roofline": {
-            "bound": "tensor", "kernel": "gemm_i8_tcgen05_kernel (six linears of the block)",
+            "bound": "tensor", "kernel": "gemm_i8_tcgen05_pair_kernel (six linears of the block, CTA pairs)",
             "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
             "frac": (achieved / int8_peak) if achieved else None,
             "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}): int8 tensor rate is twice bf16",
@@ -350,8 +350,8 @@ def run_b200(args):
             "launches_timed": n_gemm, "avg_launch_ms": gemm_ms / n_gemm if n_gemm else None,
             "ops_per_launch_avg": ops_per_launch,
             # ncu capture of the q/k/v-shape launch (16384 x 4096 x 4096, int8 out): 84.0 MB read +
-            # 42.0 MB written to DRAM against 151 MB algorithmic (part of the output was still in L2)
-            "traffic": (126.0e6 if (world == 1 and not args.small) else None),
+            # 43.1 MB written to DRAM against 151 MB algorithmic (part of the output was still in L2)
+            "traffic": (127.1e6 if (world == 1 and not args.small) else None),
             "traffic_note": "dram__bytes_read+write of one q/k/v-shape launch (profiles/gemm_i8_tcgen05_16384x4096x4096.md); "
                             "algorithmic bytes of that launch: 151 MB",
         },
