@@ -42,6 +42,8 @@ def parse():
     ap.add_argument("--small", action="store_true", help="reduced shapes (profiling under ncu)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-groups", type=int, default=4,
+                    help="host-buffer run: sequence groups per step moving through the upload/compute/download ring")
     ap.add_argument("--tp-mode", default="fused", choices=["fused", "dma", "push", "nccl"],
                     help="N>1: 'push' = row-parallel GEMMs store their tiles into the owners' buffers from the epilogue, "
                          "owner adds locally inside the LayerNorm kernel; 'fused' = LayerNorm kernel pulls the partial "
@@ -317,7 +319,7 @@ def run_b200(args):
     # ---- end to end from host buffers: H2D inputs, block, D2H outputs, three streams
     e2e = None
     if not args.no_e2e:  # (host-buffer run uses the all-reduce form of the step at every N)
-        e2e = run_e2e(block, residual_h, acc_h, cfg, dev, world, dist, max(3, args.steps), barrier)
+        e2e = run_e2e(block, residual_h, acc_h, cfg, dev, world, dist, max(3, args.steps), barrier, args.e2e_groups)
 
     if rank != 0:
         if world > 1:
@@ -366,7 +368,7 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
-def run_e2e(block, residual_h, acc_h, cfg, dev, world, dist, steps, barrier):
+def run_e2e(block, residual_h, acc_h, cfg, dev, world, dist, steps, barrier, want_groups=4):
     """Same block, inputs in pinned host memory: every step copies both inputs to the
     device, runs the block and copies both outputs back.  A step moves as groups of
     sequences (sequences are independent of one another in a decoder block): uploads,
@@ -374,7 +376,9 @@ def run_e2e(block, residual_h, acc_h, cfg, dev, world, dist, steps, barrier):
     one group's upload and another's download overlap a third's kernels, and the
     pipeline's fill and drain cost one group, not one step."""
     tokens = cfg["batch"] * cfg["seq"]
-    groups = 4 if cfg["batch"] % 4 == 0 else (2 if cfg["batch"] % 2 == 0 else 1)
+    groups = max(1, min(want_groups, cfg["batch"]))
+    while cfg["batch"] % groups:
+        groups -= 1
     gb = cfg["batch"] // groups          # sequences per group
     gt = gb * cfg["seq"]                 # tokens per group
     ring = 3
