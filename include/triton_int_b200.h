@@ -42,7 +42,11 @@ typedef enum {
   TI_EPI_SCALE = 1,           /* C = cast(alpha*f32(acc))        kernels/linear.py:107; kernels/bmm.py:414,562,710 */
   TI_EPI_SCALE_BIAS = 2,      /* C = cast(beta*f32(bias) + alpha*f32(acc))   kernels/linear.py:225-227,247,254,674,817 */
   TI_EPI_SCALE_BIAS_RELU = 3, /* C = max(cast_i8(...), 0)        kernels/linear.py:396 */
-  TI_EPI_GELU_Q = 4           /* C = cast_i8(gelu_tanh(alpha*f32(acc) + bias) * beta)   kernels/fused.py:184-187 */
+  TI_EPI_GELU_Q = 4,          /* C = cast_i8(gelu_tanh(alpha*f32(acc) + bias) * beta)   kernels/fused.py:184-187 */
+  TI_EPI_DQ_ADD = 5           /* C(fp32) = fma(f32(acc + bias_i32), alpha, residual[m,n]): the dequantise + residual-add
+                                 front half of DQ_Add_LayerNorm_Q (functional/fused.py:6-15, nn/fused.py:59-78) done by
+                                 the GEMM that produced acc; C is then the new residual stream and the input of a plain
+                                 LayerNorm -> int8.  fp32 output, batch == 1, tensor-map path only. */
 } ti_epilogue;
 
 typedef enum { TI_PATH_AUTO = 0, TI_PATH_TCGEN05 = 1, TI_PATH_GENERIC = 2 } ti_gemm_path;
@@ -81,6 +85,10 @@ typedef struct {
    * kernel adds them (exactly) and applies the epilogue.  NULL / 0: never split. */
   void* workspace;
   int64_t workspace_bytes;
+  /* TI_EPI_DQ_ADD only: fp32 [m, n] residual read by the epilogue, row stride in elements
+   * (a multiple of 4), columns contiguous, 16-byte aligned; must not overlap c. */
+  const float* residual;
+  int64_t residual_stride_m;
 } ti_gemm_params;
 
 /* Bytes of workspace with which ti_gemm_i8 would split K for this problem on the

@@ -17,7 +17,7 @@ from . import _build
 TI_OK, TI_ERR_SHAPE, TI_ERR_DTYPE, TI_ERR_ALIGN, TI_ERR_DEVICE, TI_ERR_TIMEOUT, TI_ERR_CUDA, TI_ERR_UNSUPPORTED = range(8)
 TI_I8, TI_I32, TI_F32, TI_F16, TI_BF16 = range(5)
 ROUND_RNE_SAT, ROUND_TRUNC_WRAP = 0, 1
-EPI_I32, EPI_SCALE, EPI_SCALE_BIAS, EPI_SCALE_BIAS_RELU, EPI_GELU_Q = range(5)
+EPI_I32, EPI_SCALE, EPI_SCALE_BIAS, EPI_SCALE_BIAS_RELU, EPI_GELU_Q, EPI_DQ_ADD = range(6)
 PATH_AUTO, PATH_TCGEN05, PATH_GENERIC = range(3)
 
 DTYPE_CODE = {torch.int8: TI_I8, torch.int32: TI_I32, torch.float32: TI_F32,
@@ -39,6 +39,7 @@ class GemmParams(C.Structure):
         ("rounding", C.c_int32), ("path", C.c_int32), ("causal", C.c_int32),
         ("stream", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
+        ("residual", C.c_void_p), ("residual_stride_m", C.c_int64),
     ]
 
 

@@ -47,6 +47,8 @@ struct Params {
   int c_tma_ok;  // map_c is valid: output written with tensor stores
   int b_mn_major;           // B is [K, N] with N contiguous ("s8t" second operand): MN-major smem tiles
   int rows_per_rank, rank;  // scatter mode: rows [r*rows_per_rank, ...) belong to rank r; this rank's slot index
+  const float* residual;    // TI_EPI_DQ_ADD: fp32 [m, n] added after the dequantisation
+  int64_t res_stride_m;
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -401,8 +403,33 @@ __device__ __forceinline__ float gelu_q_fast(float x, float scale) {
 // scale+bias epilogues; raw int32 bits for the int32 epilogue) or is null.
 template <typename OutT, int epilogue>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const float* bias_c, float alpha, float beta,
-                                               int rounding, uint32_t (&vw)[8 * sizeof(OutT)]) {
+                                               int rounding, uint32_t (&vw)[8 * sizeof(OutT)],
+                                               const float* res = nullptr, int res_n = 0) {
   float f[32];
+  if constexpr (epilogue == TI_EPI_DQ_ADD) {
+    // residual + alpha * (acc + bias_i32) with one rounding: the arithmetic the dequantising
+    // LayerNorm kernel does per element, so the two forms return the same bits.
+    // `res` points at this thread's 32 residual values (res_n of them exist), or is null.
+    float rv[32];
+    if (res && res_n >= 32) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 t = __ldcs(reinterpret_cast<const float4*>(res + j));
+        rv[j] = t.x; rv[j + 1] = t.y; rv[j + 2] = t.z; rv[j + 3] = t.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) rv[j] = (res && j < res_n) ? res[j] : 0.f;
+    }
+    if constexpr (std::is_same<OutT, float>::value) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int a = (int)r[j] + (bias_c ? __float_as_int(bias_c[j]) : 0);
+        vw[j] = __float_as_uint(__fmaf_rn(__int2float_rn(a), alpha, rv[j]));
+      }
+    }
+    return;
+  }
   if constexpr (epilogue == TI_EPI_I32) {
     if constexpr (std::is_same<OutT, int32_t>::value) {
 #pragma unroll
@@ -702,7 +729,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorM
           const int col = col0 + c;
           float bv = 0.f;
           if (col < p.n) {
-            if constexpr (EPI == TI_EPI_I32) {
+            if constexpr (EPI == TI_EPI_I32 || EPI == TI_EPI_DQ_ADD) {
               bv = __int_as_float(((const int32_t*)p.bias)[col]);
             } else {
               bv = load_bias_f32(p.bias, p.bias_dtype, col);
@@ -734,8 +761,14 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* pa, const CUtensorM
         const int ccol = half * HALF_N + chunk * 32;  // column inside the tile
         const int col = col0 + ccol;
         alignas(16) uint32_t vw[8 * ESZ];
-        if (col < p.n)
-          epilogue_chunk<OutT, EPI>(r, has_bias ? bias_s + ccol : nullptr, alpha, beta, p.rounding, vw);
+        if (col < p.n) {
+          if constexpr (EPI == TI_EPI_DQ_ADD) {
+            const float* res = row_ok ? p.residual + (int64_t)row * p.res_stride_m + col : nullptr;
+            epilogue_chunk<OutT, EPI>(r, has_bias ? bias_s + ccol : nullptr, alpha, beta, p.rounding, vw, res, p.n - col);
+          } else {
+            epilogue_chunk<OutT, EPI>(r, has_bias ? bias_s + ccol : nullptr, alpha, beta, p.rounding, vw);
+          }
+        }
         if (p.c_tma_ok) {
           const int sub = chunk % CHUNKS_PER_BUF;
           if (sub == 0) {
@@ -970,6 +1003,7 @@ int launch_cfg(const ti_gemm_params& g, int num_sms) {
   p.rounding = g.rounding;
   p.causal = g.causal;
   p.rows_per_rank = 0; p.rank = 0;
+  p.residual = g.residual; p.res_stride_m = g.residual_stride_m;
   const int64_t esz = (int64_t)sizeof(OutT);
   p.c_vec_ok = (g.c_stride_n == 1) && (((uintptr_t)g.c & 15) == 0) && ((g.c_stride_m * esz) % 16 == 0) &&
                ((g.c_stride_batch * esz) % 16 == 0);
@@ -1018,6 +1052,7 @@ int launch_pair_cfg(const ti_gemm_params& g, int num_sms) {
   p.num_kb = (int)((g.k + BK - 1) / BK);
   p.bias_dtype = g.bias_dtype; p.epilogue = g.epilogue; p.rounding = g.rounding; p.causal = 0;
   p.b_mn_major = 0; p.rows_per_rank = 0; p.rank = 0;
+  p.residual = g.residual; p.res_stride_m = g.residual_stride_m;
   const int64_t esz = (int64_t)sizeof(OutT);
   p.c_vec_ok = (g.c_stride_n == 1) && (((uintptr_t)g.c & 15) == 0) && ((g.c_stride_m * esz) % 16 == 0) &&
                ((g.c_stride_batch * esz) % 16 == 0);
@@ -1088,6 +1123,7 @@ int launch_scatter_cfg(const ti_gemm_params& g, const ti_gemm_scatter& sc, int n
   p.bias_dtype = TI_I32; p.epilogue = TI_EPI_I32; p.rounding = g.rounding; p.causal = 0;
   p.c_vec_ok = 1; p.c_tma_ok = 1;
   p.rows_per_rank = (int)sc.rows_per_rank; p.rank = sc.rank; p.b_mn_major = 0;
+  p.residual = nullptr; p.res_stride_m = 0;
   auto kern = gemm_i8_tcgen05_scatter_kernel<BN, STAGES>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -1184,7 +1220,7 @@ splitk_reduce_kernel(const ReduceParams p) {
 // than half of the SMs idle, K at least 8 stages long, N a multiple of 4.  The split count
 // divides the number of 128-byte K blocks so every part is whole.
 inline int pick_splits(const ti_gemm_params& g, int num_sms) {
-  if (g.batch != 1 || g.causal || (g.n % 4) != 0 || (g.k % BK) != 0 || b_is_mn_major(g)) return 1;
+  if (g.batch != 1 || g.causal || (g.n % 4) != 0 || (g.k % BK) != 0 || b_is_mn_major(g) || g.epilogue == TI_EPI_DQ_ADD) return 1;
   const int bn = g.n > 128 ? 256 : (g.n > 64 ? 128 : 64);
   const int64_t tiles = ((g.m + BM - 1) / BM) * ((g.n + bn - 1) / bn);
   const int64_t kb = g.k / BK;
@@ -1259,6 +1295,7 @@ inline int launch_plain(const ti_gemm_params& g, int num_sms) {
     case TI_F32:
       if (ep == TI_EPI_SCALE) return launch_epi<float, TI_EPI_SCALE>(g, num_sms);
       if (ep == TI_EPI_SCALE_BIAS) return launch_epi<float, TI_EPI_SCALE_BIAS>(g, num_sms);
+      if (ep == TI_EPI_DQ_ADD) return launch_epi<float, TI_EPI_DQ_ADD>(g, num_sms);
       break;
     case TI_F16:
       if (ep == TI_EPI_SCALE) return launch_epi<__half, TI_EPI_SCALE>(g, num_sms);

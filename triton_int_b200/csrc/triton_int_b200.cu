@@ -114,7 +114,16 @@ int ti_gemm_i8(const ti_gemm_params* g) {
   // dtype / epilogue combinations
   const int od = g->out_dtype, ep = g->epilogue;
   if (od < TI_I8 || od > TI_BF16) { set_error("gemm: bad out dtype %d", od); return TI_ERR_DTYPE; }
-  if (ep < TI_EPI_I32 || ep > TI_EPI_GELU_Q) { set_error("gemm: bad epilogue %d", ep); return TI_ERR_UNSUPPORTED; }
+  if (ep < TI_EPI_I32 || ep > TI_EPI_DQ_ADD) { set_error("gemm: bad epilogue %d", ep); return TI_ERR_UNSUPPORTED; }
+  if (ep == TI_EPI_DQ_ADD) {
+    if (od != TI_F32) { set_error("gemm: the dequantise + residual epilogue stores fp32"); return TI_ERR_DTYPE; }
+    if (g->bias && g->bias_dtype != TI_I32) { set_error("gemm: the dequantise + residual epilogue takes an int32 bias"); return TI_ERR_DTYPE; }
+    if (g->batch != 1 || g->causal) { set_error("gemm: the dequantise + residual epilogue is for single (non-batched) linears"); return TI_ERR_UNSUPPORTED; }
+    if (!g->residual || ((uintptr_t)g->residual & 15) || (g->residual_stride_m & 3) || g->residual_stride_m < g->n) {
+      set_error("gemm: residual must be a 16-byte aligned fp32 [m, n] matrix with a row stride that is a multiple of 4 elements");
+      return TI_ERR_ALIGN;
+    }
+  }
   if (ep == TI_EPI_I32 && od != TI_I32) { set_error("gemm: the raw accumulator epilogue stores int32"); return TI_ERR_DTYPE; }
   if (ep == TI_EPI_I32 && g->bias && g->bias_dtype != TI_I32) { set_error("gemm: int32 epilogue takes an int32 bias"); return TI_ERR_DTYPE; }
   if ((ep == TI_EPI_SCALE_BIAS_RELU || ep == TI_EPI_GELU_Q) && od != TI_I8) {
@@ -137,6 +146,14 @@ int ti_gemm_i8(const ti_gemm_params* g) {
     return TI_ERR_ALIGN;
   }
   if (g->path == TI_PATH_GENERIC) fast = false;
+  if (ep == TI_EPI_DQ_ADD) {
+    if (!is_device_ptr(g->residual)) { set_error("gemm: residual must be a device pointer"); return TI_ERR_DEVICE; }
+    if (!fast) {
+      set_error("gemm: the dequantise + residual epilogue exists on the tensor-map path only "
+                "(K-contiguous operands on 16-byte boundaries); use TI_EPI_I32 and ti_layernorm otherwise");
+      return TI_ERR_UNSUPPORTED;
+    }
+  }
   return fast ? ti::tc::launch(*g, di.sms) : ti::generic::launch(*g);
 }
 

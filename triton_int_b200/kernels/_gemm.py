@@ -31,7 +31,7 @@ def scale_tensor(s, device) -> torch.Tensor:
 
 
 def gemm(a3, b3, b_is_nk, out_dtype, epilogue, *, bias=None, alpha=None, beta=None, out=None,
-         causal=False, rounding=None, path=None):
+         causal=False, rounding=None, path=None, residual=None):
     """a3: int8 [B,M,K] view (any strides).  b3: int8 [B,N,K] (b_is_nk) or [B,K,N].
     Returns the [B,M,N] result (written into `out` when given)."""
     _lib.require_cuda(a3, b3, bias, out)
@@ -80,6 +80,15 @@ def gemm(a3, b3, b_is_nk, out_dtype, epilogue, *, bias=None, alpha=None, beta=No
     p.rounding = config.rounding_mode() if rounding is None else rounding
     p.path = config.gemm_path() if path is None else path
     p.causal = 1 if causal else 0
+    if residual is not None:
+        # dequantise + residual-add epilogue: fp32 [M, N], columns contiguous
+        _lib.require_cuda(residual)
+        if residual.dtype != torch.float32 or residual.dim() != 2 or tuple(residual.shape) != (M, N) or B != 1:
+            raise AssertionError("residual must be an fp32 [M, N] matrix (non-batched linear)")
+        if residual.stride(1) != 1:
+            residual = residual.contiguous()
+        keep.append(residual)
+        p.residual, p.residual_stride_m = residual.data_ptr(), residual.stride(0)
     with torch.cuda.device(dev):
         p.stream = _lib.current_stream_ptr(dev)
         if B == 1 and M <= 256:

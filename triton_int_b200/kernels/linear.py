@@ -23,9 +23,9 @@ def _flatten(a, b):
     return lead, a2.unsqueeze(0), b.unsqueeze(0)
 
 
-def _linear(a, b, out_dtype, epilogue, bias=None, alpha=None, beta=None, out=None):
+def _linear(a, b, out_dtype, epilogue, bias=None, alpha=None, beta=None, out=None, residual=None):
     lead, a3, b3 = _flatten(a, b)
-    c = gemm(a3, b3, True, out_dtype, epilogue, bias=bias, alpha=alpha, beta=beta, out=out)
+    c = gemm(a3, b3, True, out_dtype, epilogue, bias=bias, alpha=alpha, beta=beta, out=out, residual=residual)
     return c.view(*lead, b.shape[0])
 
 
@@ -67,3 +67,14 @@ def linear_a8_w8_bfp32_ofp32(a, b, bias, scale_a, scale_b, out=None, dtype=None)
     if dtype is None:
         dtype = out.dtype if out is not None else bias.dtype
     return _linear(a, b, dtype, _lib.EPI_SCALE_BIAS, bias=bias, alpha=scale_a, beta=scale_b, out=out)
+
+
+def linear_a8_w8_b32_dq_add_ofp32(a, b, bias, dq_scale, residual, out=None):
+    """fp32(residual + dq_scale * (acc + bias_i32)): a row-parallel linear whose epilogue does the
+    dequantise + residual-add front half of DQ_Add_LayerNorm_Q (reference
+    functional/fused.py:6-15, nn/fused.py:59-78), bit for bit what ``dq_add_layernorm_q``
+    would return as its residual output; the result feeds ``layer_norm_fwd_fused_single_pass_q``.
+    No counterpart kernel in the reference.  ``residual`` is fp32 with the output's shape."""
+    n = b.shape[0]
+    res2 = residual.reshape(-1, n)
+    return _linear(a, b, torch.float32, _lib.EPI_DQ_ADD, bias=bias, alpha=dq_scale, out=out, residual=res2)

@@ -28,8 +28,9 @@ from __future__ import annotations
 import torch
 
 from ..kernels.bmm import bmm_s8t_s8n_f32t, bmm_s8t_s8n_s8t
-from ..kernels.fused import attention_i8, causal_softmax_q, dq_add_layernorm_q, linear_a8_w8_bfp32_ofp32_GeLu_Q
-from ..kernels.linear import linear_a8_w8_b8_o8, linear_a8_w8_b32_o32
+from ..kernels.fused import (attention_i8, causal_softmax_q, dq_add_layernorm_q, layer_norm_fwd_fused_single_pass_q,
+                             linear_a8_w8_bfp32_ofp32_GeLu_Q)
+from ..kernels.linear import linear_a8_w8_b8_o8, linear_a8_w8_b32_dq_add_ofp32, linear_a8_w8_b32_o32
 
 
 def shard_rows(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
@@ -53,7 +54,7 @@ class Int8DecoderBlock(torch.nn.Module):
     when world == 1)."""
 
     def __init__(self, params, rank: int = 0, world: int = 1, reduce_fn=None, causal_skip: bool = True,
-                 fused_attention: bool = True):
+                 fused_attention: bool = True, fuse_dq_add: bool = True):
         super().__init__()
         meta = params["meta"]
         self.hidden, self.heads, self.ffn = meta["hidden"], meta["heads"], meta["ffn"]
@@ -67,6 +68,8 @@ class Int8DecoderBlock(torch.nn.Module):
         # fused attention keeps S and P on chip; the unfused form (three operators of the
         # reference interface) is kept for comparison
         self.fused_attention = fused_attention and self.head_dim == 128
+        # one rank: out_proj's epilogue does the dequantise + residual add of the LayerNorm step that follows
+        self.fuse_dq_add = fuse_dq_add and world == 1 and self.hidden % 16 == 0
         reg = self.register_buffer
         reg("ln1_w", params["ln1_w"].clone()); reg("ln1_b", params["ln1_b"].clone())
         reg("ln2_w", params["ln2_w"].clone()); reg("ln2_b", params["ln2_b"].clone())
@@ -116,9 +119,15 @@ class Int8DecoderBlock(torch.nn.Module):
         res1, x8 = dq_add_layernorm_q(prev_acc, self.prev_scale, residual, self.ln1_w, self.ln1_b, self.eps,
                                       bias_int32=prev_bias)
         attn = self.attention(x8, batch, seq)
-        out_acc = self.reduce_fn(linear_a8_w8_b32_o32(attn, self.out_w, None))
-        res2, h8 = dq_add_layernorm_q(out_acc, self.out_scale, res1, self.ln2_w, self.ln2_b, self.eps,
-                                      bias_int32=self.out_bias)
+        if self.world == 1 and self.fuse_dq_add:
+            # one rank: nothing to sum across ranks, so out_proj's epilogue dequantises and adds the
+            # residual itself and the LayerNorm kernel reads 4 bytes per element instead of 8 (same bits)
+            res2 = linear_a8_w8_b32_dq_add_ofp32(attn, self.out_w, self.out_bias, self.out_scale, res1)
+            h8 = layer_norm_fwd_fused_single_pass_q(res2, self.ln2_w, self.ln2_b, self.eps)
+        else:
+            out_acc = self.reduce_fn(linear_a8_w8_b32_o32(attn, self.out_w, None))
+            res2, h8 = dq_add_layernorm_q(out_acc, self.out_scale, res1, self.ln2_w, self.ln2_b, self.eps,
+                                          bias_int32=self.out_bias)
         g8 = linear_a8_w8_bfp32_ofp32_GeLu_Q(h8, self.fc1_w, self.fc1_bias, self.fc1_alpha, self.fc1_mul)
         fc2_acc = self.reduce_fn(linear_a8_w8_b32_o32(g8, self.fc2_w, None))
         return res2, fc2_acc
